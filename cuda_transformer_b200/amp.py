@@ -1,0 +1,440 @@
+"""Host side of the AMP optimizer step, over the C ABI of libb200amp.so.
+
+Two layers:
+
+* free functions with the reference's names and argument meaning
+  (cuda/kernels/fast.h:136-166, cuda/graph.h:14-30): initial_state, begin_step,
+  unscale_and_norm, finalize_step, adamw_multi, lr_on_gpu, cast_to_x, CudaGraph. They
+  take raw device pointers (ints) or torch tensors and raise B200AmpError where the
+  reference would print and exit(1) (cuda/common.h:10-20).
+
+* AmpOptimizer: what FastGPT keeps for its optimizer (cuda/gpt_fast.cu:96-149,
+  245-253, 438-467): the arenas, the tensor table, the device-resident step state and
+  history ring, reset / set_params / optimizer_step / read_state, with the fp16
+  gradient arena the native kernels read. ShardedAmpOptimizer is the ZeRO-1 form over
+  torch.distributed: reduce-scatter of fp16 gradients, the two passes on the rank's
+  shard, an all-gather of the 16-byte {norm^2, flag} pairs, and an in-place
+  all-gather of the fp16 weights.
+
+torch is used for device memory, streams and the process group only; every
+arithmetic step runs in the CUDA kernels of the library.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import B200AmpError, ScheduleConfig, StepState, TensorInfo, check
+from .layout import ParamSlot, padded, shard_range, tensor_table
+
+__all__ = [
+    "StepState", "ScheduleConfig", "TensorInfo", "B200AmpError",
+    "initial_state", "begin_step", "unscale_and_norm", "finalize_step", "adamw_multi", "lr_on_gpu",
+    "cast_to_x", "CudaGraph", "AmpOptimizer", "Zero1Step", "ShardedAmpOptimizer", "make_schedule",
+    "pass1_f16", "pass1_finalize_f16", "finalize_sums", "pass2_f16", "step_f16",
+]
+
+
+def _ptr(x) -> Optional[int]:
+    """Device pointer of a tensor (or pass an int / None through)."""
+    if x is None:
+        return None
+    if isinstance(x, torch.Tensor):
+        if not x.is_cuda:
+            raise ValueError("expected a CUDA tensor: the step has no CPU path")
+        if not x.is_contiguous():
+            raise ValueError("expected a contiguous tensor")
+        return x.data_ptr()
+    return int(x)
+
+
+def _stream(stream) -> int:
+    """cudaStream_t handle: a torch stream, a raw handle, or None = torch's current stream."""
+    if stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    if isinstance(stream, torch.cuda.Stream):
+        return stream.cuda_stream
+    return int(stream)
+
+
+def make_schedule(lr=6e-4, min_lr=6e-4, warmup_steps=0, max_steps=1 << 30, beta1=0.9, beta2=0.95,
+                  weight_decay=0.1, grad_clip=1.0, growth_interval=2000, dynamic_scale=1,
+                  decay_steps=0) -> ScheduleConfig:
+    """A ScheduleConfig; the defaults are the flat-lr setting the reference's tests use
+    (cuda/tests/test_fast.cu:85-92) with the reference's AdamW numbers (reference/config.py)."""
+    return ScheduleConfig(lr, min_lr, warmup_steps, max_steps, beta1, beta2, weight_decay, grad_clip,
+                          growth_interval, dynamic_scale, decay_steps)
+
+
+# ------------------------------------------------------------------ the reference's launchers
+
+def initial_state(scale: float) -> StepState:
+    """cuda/kernels/scaler.cu:21-29."""
+    st = StepState()
+    check(_lib.load().b200amp_initial_state(scale, C.byref(st)))
+    return st
+
+
+def begin_step(st, stream=None) -> None:
+    """cuda/kernels/scaler.cu:173-177."""
+    check(_lib.load().b200amp_begin_step(_ptr(st), _stream(stream)))
+
+
+def unscale_and_norm(grads, n: int, st, partial, stream=None) -> None:
+    """cuda/kernels/scaler.cu:179-184: fp32 grads *= inv_scale in place, flag, partial[512]."""
+    check(_lib.load().b200amp_unscale_and_norm_f32(_ptr(grads), n, _ptr(st), _ptr(partial), _stream(stream)))
+
+
+def finalize_step(st, partial, cfg: ScheduleConfig, history=None, history_len: int = 0, stream=None) -> None:
+    """cuda/kernels/scaler.cu:186-192."""
+    check(_lib.load().b200amp_finalize_step(_ptr(st), _ptr(partial), C.byref(cfg), _ptr(history), history_len,
+                                            _stream(stream)))
+
+
+def adamw_multi(params, params_x, grads, m, v, n: int, tensors, ntensors: int, st, beta1: float, beta2: float,
+                eps: float, stream=None) -> None:
+    """cuda/kernels/adamw_multi.cu:93-108 (unscaled fp32 gradients; params_x may be None)."""
+    check(_lib.load().b200amp_adamw_multi_f32(_ptr(params), _ptr(params_x), _ptr(grads), _ptr(m), _ptr(v), n,
+                                              _ptr(tensors), ntensors, _ptr(st), beta1, beta2, eps,
+                                              _stream(stream)))
+
+
+def lr_on_gpu(step: int, cfg: ScheduleConfig) -> float:
+    """cuda/kernels/scaler.cu:100-110."""
+    out = C.c_double()
+    check(_lib.load().b200amp_lr_on_gpu(step, C.byref(cfg), C.byref(out)))
+    return out.value
+
+
+def cast_to_x(out_f16, inp_f32, n: int, stream=None) -> None:
+    """cuda/kernels/fused.cu:319-323 in the fp16 build."""
+    check(_lib.load().b200amp_cast_to_x(_ptr(out_f16), _ptr(inp_f32), n, _stream(stream)))
+
+
+# ------------------------------------------------------------------ native entry points
+
+def pass1_f16(grads16, n: int, st, workspace, stream=None) -> None:
+    check(_lib.load().b200amp_pass1_f16(_ptr(grads16), n, _ptr(st), _ptr(workspace), _stream(stream)))
+
+
+def pass1_finalize_f16(grads16, n: int, st, workspace, cfg: ScheduleConfig, history=None, history_len: int = 0,
+                       stream=None) -> None:
+    check(_lib.load().b200amp_pass1_finalize_f16(_ptr(grads16), n, _ptr(st), _ptr(workspace), C.byref(cfg),
+                                                 _ptr(history), history_len, _stream(stream)))
+
+
+def finalize_sums(st, sums, nranks: int, cfg: ScheduleConfig, history=None, history_len: int = 0,
+                  stream=None) -> None:
+    check(_lib.load().b200amp_finalize_sums(_ptr(st), _ptr(sums), nranks, C.byref(cfg), _ptr(history),
+                                            history_len, _stream(stream)))
+
+
+def pass2_f16(master, m, v, grads16, weights16, n: int, arena_offset: int, tensors, ntensors: int, st,
+              beta1: float, beta2: float, eps: float, stream=None) -> None:
+    check(_lib.load().b200amp_pass2_f16(_ptr(master), _ptr(m), _ptr(v), _ptr(grads16), _ptr(weights16), n,
+                                        arena_offset, _ptr(tensors), ntensors, _ptr(st), beta1, beta2, eps,
+                                        _stream(stream)))
+
+
+def step_f16(master, m, v, grads16, weights16, n: int, tensors, ntensors: int, st, workspace,
+             cfg: ScheduleConfig, history, history_len: int, beta1: float, beta2: float, eps: float,
+             stream=None) -> None:
+    check(_lib.load().b200amp_step_f16(_ptr(master), _ptr(m), _ptr(v), _ptr(grads16), _ptr(weights16), n,
+                                       _ptr(tensors), ntensors, _ptr(st), _ptr(workspace), C.byref(cfg),
+                                       _ptr(history), history_len, beta1, beta2, eps, _stream(stream)))
+
+
+class CudaGraph:
+    """capture / launch / ready, as cuda/graph.h:14-30. The body runs once in capture
+    mode (nothing executes) and is replayed by launch()."""
+
+    def __init__(self) -> None:
+        self._handle = C.c_void_p()
+
+    def ready(self) -> bool:
+        return bool(self._handle)
+
+    def capture(self, stream, body) -> None:
+        lib = _lib.load()
+        if self.ready():
+            check(lib.b200amp_graph_destroy(self._handle))
+            self._handle = C.c_void_p()
+        s = _stream(stream)
+        check(lib.b200amp_graph_begin_capture(s))
+        try:
+            body()
+        finally:
+            status = lib.b200amp_graph_end_capture(s, C.byref(self._handle))
+        check(status)
+
+    def launch(self, stream=None) -> None:
+        check(_lib.load().b200amp_graph_launch(self._handle, _stream(stream)))
+
+    def __del__(self) -> None:
+        try:
+            if self._handle:
+                _lib.load().b200amp_graph_destroy(self._handle)
+                self._handle = C.c_void_p()
+        except Exception:
+            pass
+
+
+# ------------------------------------------------------------------ arena owners
+
+def _upload_struct(struct_obj, device) -> torch.Tensor:
+    raw = bytes(struct_obj)
+    host = torch.frombuffer(bytearray(raw), dtype=torch.uint8)
+    return host.to(device)
+
+
+def _tensor_table_device(table: Sequence[Tuple[int, int, int]], device) -> torch.Tensor:
+    arr = (TensorInfo * len(table))(*[TensorInfo(o, c, d) for o, c, d in table])
+    host = torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8)
+    return host.to(device)
+
+
+class AmpOptimizer:
+    """The optimizer state of one GPU that holds the whole arena.
+
+    Arenas (flat, in param_layout order, cuda/gpt_fast.cu:96-115): master, m, v (fp32),
+    weights16 (fp16 copy the GEMMs read) and grads16 (fp16, loss-scaled, written by the
+    caller before each step). Step state, history ring and the pass-1 workspace live in
+    device memory; nothing crosses to the host inside optimizer_step().
+    """
+
+    def __init__(self, slots: List[ParamSlot], cfg: ScheduleConfig, eps: float = 1e-8,
+                 loss_scale: float = 65536.0, history_len: int = 256, device="cuda:0",
+                 extra_tensors: Sequence[Tuple[int, int, int]] = ()):
+        self.lib = _lib.load()
+        check(self._with_device(device, self.lib.b200amp_device_check))
+        self.device = torch.device(device)
+        self.slots = slots
+        self.n_params = slots[-1].offset + slots[-1].count
+        self.n = padded(self.n_params)
+        self.sched = cfg
+        self.beta1, self.beta2, self.eps = cfg.beta1, cfg.beta2, eps
+        self.history_len = history_len
+        table = list(tensor_table(slots)) + list(extra_tensors)
+        if self.n > self.n_params and not extra_tensors:
+            table.append((self.n_params, self.n - self.n_params, 0))       # zero padding: never decayed
+        self.ntensors = len(table)
+        with torch.cuda.device(self.device):
+            self.tensors = _tensor_table_device(table, self.device)
+            self.master = torch.zeros(self.n, dtype=torch.float32, device=self.device)
+            self.m = torch.zeros_like(self.master)
+            self.v = torch.zeros_like(self.master)
+            self.weights16 = torch.zeros(self.n, dtype=torch.float16, device=self.device)
+            self.grads16 = torch.zeros(self.n, dtype=torch.float16, device=self.device)
+            self.state = torch.zeros(C.sizeof(StepState), dtype=torch.uint8, device=self.device)
+            self.history = torch.zeros(C.sizeof(StepState) * history_len, dtype=torch.uint8, device=self.device)
+            self.workspace = torch.zeros(self.lib.b200amp_workspace_bytes(), dtype=torch.uint8, device=self.device)
+        self.reset(loss_scale)
+
+    @staticmethod
+    def _with_device(device, fn):
+        with torch.cuda.device(torch.device(device)):
+            return fn()
+
+    def reset(self, loss_scale: float) -> None:
+        """m = v = grads = 0 and a fresh state (cuda/gpt_fast.cu:245-253)."""
+        self.m.zero_()
+        self.v.zero_()
+        self.grads16.zero_()
+        self.history.zero_()
+        self.workspace.zero_()
+        self.write_state(initial_state(loss_scale))
+
+    def write_state(self, st: StepState) -> None:
+        self.state.copy_(_upload_struct(st, self.device))
+        torch.cuda.current_stream(self.device).synchronize()
+
+    def set_params(self, host_params: torch.Tensor) -> None:
+        """Upload fp32 parameters and rebuild the fp16 copy (cuda/gpt_fast.cu:274-286)."""
+        flat = host_params.reshape(-1).to(torch.float32)
+        if flat.numel() != self.n_params:
+            raise ValueError(f"{flat.numel()} parameters given, the arena holds {self.n_params}")
+        self.master.zero_()
+        self.master[: self.n_params].copy_(flat)
+        with torch.cuda.device(self.device):
+            cast_to_x(self.weights16, self.master, self.n)
+
+    def optimizer_step(self, stream=None) -> None:
+        """The two launches of the step (the place of cuda/gpt_fast.cu:438-450)."""
+        with torch.cuda.device(self.device):
+            step_f16(self.master, self.m, self.v, self.grads16, self.weights16, self.n, self.tensors,
+                     self.ntensors, self.state, self.workspace, self.sched, self.history, self.history_len,
+                     self.beta1, self.beta2, self.eps, stream)
+
+    def read_state(self) -> StepState:
+        """Sync + D2H of the 60-byte state (cuda/gpt_fast.cu:461-467)."""
+        raw = bytes(self.state.cpu().numpy().tobytes())
+        return StepState.from_buffer_copy(raw)
+
+    def read_history(self) -> List[StepState]:
+        raw = self.history.cpu().numpy().tobytes()
+        size = C.sizeof(StepState)
+        return [StepState.from_buffer_copy(raw[i * size:(i + 1) * size]) for i in range(self.history_len)]
+
+
+class Zero1Step:
+    """Orchestration of the ZeRO-1 step over a torch.distributed process group.
+
+    Every rank holds the full fp16 gradient arena (its own micro-batch's gradients) and
+    the full fp16 weight arena; master, m and v exist only for the rank's slice
+    [begin, end) of the arena. One step:
+        reduce-scatter(AVG) of grads16 into the rank's slice  ->  pass 1 on the slice
+        ->  all-gather of {sum of squares, flag} (16 B per rank)  ->  finalize (replicated,
+        pairs added in rank order so every rank holds identical state bits)
+        ->  pass 2 on the slice, writing fp16 weights into the slice of weights16
+        ->  in-place all-gather of weights16.
+    The inf/NaN flag and the norm are taken on the averaged gradients, as DDP +
+    GradScaler would see them.
+
+    This class owns the buffers and the collectives and is backend-agnostic (NCCL on
+    GPUs; the CPU test-suite drives it over gloo). The three compute hooks (_pass1,
+    _finalize, _pass2) are abstract here: ShardedAmpOptimizer below binds them to the
+    CUDA kernels and is the only implementation the package ships.
+    """
+
+    def __init__(self, slots: List[ParamSlot], cfg: ScheduleConfig, eps: float, loss_scale: float,
+                 history_len: int, device, group):
+        import torch.distributed as dist
+        self.dist = dist
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.slots = slots
+        self.n_params = slots[-1].offset + slots[-1].count
+        self.n = padded(self.n_params)
+        self.begin, self.end = shard_range(self.n, self.rank, self.world)
+        self.n_local = self.end - self.begin
+        self.sched = cfg
+        self.beta1, self.beta2, self.eps = cfg.beta1, cfg.beta2, eps
+        self.history_len = history_len
+        self.device = torch.device(device)
+        self.table = list(tensor_table(slots))
+        if self.n > self.n_params:
+            self.table.append((self.n_params, self.n - self.n_params, 0))      # zero padding: never decayed
+        self.ntensors = len(self.table)
+        dev = self.device
+        self.master = torch.zeros(self.n_local, dtype=torch.float32, device=dev)
+        self.m = torch.zeros_like(self.master)
+        self.v = torch.zeros_like(self.master)
+        self.weights16 = torch.zeros(self.n, dtype=torch.float16, device=dev)
+        self.grads16 = torch.zeros(self.n, dtype=torch.float16, device=dev)
+        self.grad_shard = torch.zeros(self.n_local, dtype=torch.float16, device=dev)
+        self.state = torch.zeros(C.sizeof(StepState), dtype=torch.uint8, device=dev)
+        self.history = torch.zeros(C.sizeof(StepState) * history_len, dtype=torch.uint8, device=dev)
+        self.sums_local = torch.zeros(2, dtype=torch.float64, device=dev)      # {sum of squares, flag}
+        self.sums_all = torch.zeros(2 * self.world, dtype=torch.float64, device=dev)
+        self.reset(loss_scale)
+
+    # -- compute hooks, bound by the subclass
+    def _pass1(self) -> None:
+        """grad_shard -> sums_local = {sum of squares of the unscaled slice, flag}."""
+        raise NotImplementedError
+
+    def _finalize(self) -> None:
+        """sums_all (rank-ordered pairs) -> state, history."""
+        raise NotImplementedError
+
+    def _pass2(self) -> None:
+        """AdamW on the slice; fp16 weights into weights16[begin:end]."""
+        raise NotImplementedError
+
+    def _cast_weights(self, full_fp32: torch.Tensor) -> None:
+        """weights16 = fp16(full_fp32), at set-up."""
+        raise NotImplementedError
+
+    # -- state
+    def reset(self, loss_scale: float) -> None:
+        self.m.zero_()
+        self.v.zero_()
+        self.grads16.zero_()
+        self.history.zero_()
+        self.write_state(initial_state_host(loss_scale))
+
+    def write_state(self, st: StepState) -> None:
+        self.state.copy_(torch.frombuffer(bytearray(bytes(st)), dtype=torch.uint8))
+        if self.device.type == "cuda":
+            torch.cuda.current_stream(self.device).synchronize()
+
+    def read_state(self) -> StepState:
+        return StepState.from_buffer_copy(self.state.cpu().numpy().tobytes())
+
+    def set_params(self, host_params: torch.Tensor) -> None:
+        """Every rank passes the same full fp32 parameter vector; it keeps its slice."""
+        flat = torch.zeros(self.n, dtype=torch.float32)
+        flat[: self.n_params] = host_params.reshape(-1).to(torch.float32)
+        self.master.copy_(flat[self.begin:self.end])
+        self._cast_weights(flat)
+
+    # -- collectives
+    def reduce_scatter_grads(self) -> None:
+        self.dist.reduce_scatter_tensor(self.grad_shard, self.grads16, op=self.dist.ReduceOp.AVG, group=self.group)
+
+    def gather_sums(self) -> None:
+        self.dist.all_gather_into_tensor(self.sums_all, self.sums_local, group=self.group)
+
+    def all_gather_weights(self) -> None:
+        self.dist.all_gather_into_tensor(self.weights16, self.weights16[self.begin:self.end], group=self.group)
+
+    def optimizer_step(self) -> None:
+        self.reduce_scatter_grads()
+        self._pass1()
+        self.gather_sums()
+        self._finalize()
+        self._pass2()
+        self.all_gather_weights()
+
+
+def initial_state_host(scale: float) -> StepState:
+    """initial_state() without touching the library (cuda/kernels/scaler.cu:21-29): plain field
+    assignments, used where a state is built before any device is chosen."""
+    st = StepState()
+    st.loss_scale = scale
+    st.inv_scale = 1.0 / scale
+    st.clip_coef = 1.0
+    st.decay = 1.0
+    return st
+
+
+class ShardedAmpOptimizer(Zero1Step):
+    """Zero1Step bound to the CUDA kernels: one rank per B200, NCCL process group."""
+
+    def __init__(self, slots: List[ParamSlot], cfg: ScheduleConfig, eps: float = 1e-8,
+                 loss_scale: float = 65536.0, history_len: int = 256, device=None, group=None):
+        self.lib = _lib.load()
+        device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+        if device.type != "cuda":
+            raise ValueError("ShardedAmpOptimizer runs on CUDA devices only")
+        with torch.cuda.device(device):
+            check(self.lib.b200amp_device_check())
+            super().__init__(slots, cfg, eps, loss_scale, history_len, device, group)
+            self.tensors = _tensor_table_device(self.table, self.device)
+            self.workspace = torch.zeros(self.lib.b200amp_workspace_bytes(), dtype=torch.uint8, device=self.device)
+            # pass 1 publishes {sum, flag} in the first 16 bytes of its workspace
+            self.sums_local = self.workspace[:16].view(torch.float64)
+
+    def _pass1(self) -> None:
+        pass1_f16(self.grad_shard, self.n_local, self.state, self.workspace)
+
+    def _finalize(self) -> None:
+        finalize_sums(self.state, self.sums_all, self.world, self.sched, self.history, self.history_len)
+
+    def _pass2(self) -> None:
+        pass2_f16(self.master, self.m, self.v, self.grad_shard, self.weights16[self.begin:self.end], self.n_local,
+                  self.begin, self.tensors, self.ntensors, self.state, self.beta1, self.beta2, self.eps)
+
+    def _cast_weights(self, full_fp32: torch.Tensor) -> None:
+        with torch.cuda.device(self.device):
+            full = full_fp32.to(self.device)
+            cast_to_x(self.weights16, full, self.n)
+            torch.cuda.current_stream().synchronize()
+
+    def optimizer_step(self) -> None:
+        with torch.cuda.device(self.device):
+            super().optimizer_step()

@@ -1,0 +1,570 @@
+// scaler.cu: everything of the step that comes before AdamW: the unscale, the
+// inf/NaN flag, the global gradient norm, and the finalize that turns them into
+// this step's clip coefficient, learning rate, skip decision and next loss scale,
+// all on the device with no host sync.
+//
+// Semantics follow cuda/kernels/scaler.cu of the reference (file:line cited at each
+// piece). What is different is the shape of the work:
+//   * native pass 1 reads an fp16 gradient arena (2 B/param), never writes it, and
+//     runs a persistent grid over a FIXED virtual partition of the arena, so the
+//     sum comes out bit-identical whatever the launch shape;
+//   * the last block to finish runs the finalize, so no separate 1-block launch
+//     sits between the two passes;
+//   * the compat entry points keep the reference's arguments (fp32 gradients
+//     unscaled in place, partial[512]) and its summation order.
+
+#include <climits>
+#include <cmath>
+
+#include "internal.cuh"
+
+namespace b200amp
+{
+
+// ---------------------------------------------------------------- finalize (shared)
+
+// Learning rate of a 0-based step: linear warmup, then cosine to min_lr, or (decay_steps > 0)
+// flat then 1 - sqrt down over the last decay_steps. Double throughout, the numbers of
+// cuda/kernels/scaler.cu:69-93 and reference/train.py:79-96.
+__device__ double schedule_lr(int step, const b200amp_schedule &c)
+{
+    const double peak = static_cast<double>(c.lr);
+    const double floor_lr = static_cast<double>(c.min_lr);
+    if (step < c.warmup_steps)
+    {
+        return peak * (step + 1) / c.warmup_steps;
+    }
+    if (step >= c.max_steps)
+    {
+        return floor_lr;
+    }
+    if (c.decay_steps > 0)
+    {
+        const int knee = c.max_steps - c.decay_steps;
+        if (step < knee)
+        {
+            return peak;
+        }
+        const double frac = static_cast<double>(step - knee) / c.decay_steps;
+        return floor_lr + (peak - floor_lr) * (1.0 - sqrt(frac));
+    }
+    const int span = c.max_steps - c.warmup_steps;
+    const double frac = static_cast<double>(step - c.warmup_steps) / (span > 1 ? span : 1);
+    return floor_lr + 0.5 * (1.0 + cos(3.14159265358979323846 * frac)) * (peak - floor_lr);
+}
+
+// One thread. sumsq is the squared norm of the unscaled gradients, bad the inf/NaN
+// flag. Field by field what cuda/kernels/scaler.cu:131-170 does: a skipped step
+// halves S and leaves adam_t alone; a finite one advances adam_t, computes the bias
+// corrections in double from the float betas, and doubles S after growth_interval
+// finite steps in a row.
+__device__ void finalize_state(b200amp_step_state *st, double sumsq, int bad, const b200amp_schedule &c,
+                               b200amp_step_state *history, int history_len, bool set_begin_fields)
+{
+    b200amp_step_state s = *st;
+    if (set_begin_fields)
+    {
+        s.inv_scale = 1.0f / s.loss_scale;      // of THIS step: S changes below, the unscale factor must not
+        s.found_inf = bad;
+    }
+    const float norm = static_cast<float>(sqrt(sumsq));
+    s.grad_norm = norm;
+    s.clip_coef = fminf(1.0f, c.grad_clip / (norm + 1e-6f));
+    const double lr = schedule_lr(s.step, c);
+    s.lr = static_cast<float>(lr);
+    if (s.found_inf)
+    {
+        s.skipped += 1;
+        s.good_steps = 0;
+        if (c.dynamic_scale)
+        {
+            s.loss_scale *= 0.5f;
+        }
+    }
+    else
+    {
+        s.adam_t += 1;
+        const double t = static_cast<double>(s.adam_t);
+        const double bc1 = 1.0 - pow(static_cast<double>(c.beta1), t);
+        const double bc2 = 1.0 - pow(static_cast<double>(c.beta2), t);
+        s.step_size = static_cast<float>(lr / bc1);
+        s.bc2_sqrt = static_cast<float>(sqrt(bc2));
+        s.decay = static_cast<float>(1.0 - lr * c.weight_decay);
+        s.good_steps += 1;
+        if (c.dynamic_scale && s.good_steps >= c.growth_interval)
+        {
+            s.loss_scale *= 2.0f;
+            s.good_steps = 0;
+        }
+    }
+    if (history != nullptr)
+    {
+        history[s.step % history_len] = s;
+    }
+    s.step += 1;
+    *st = s;
+}
+
+// ---------------------------------------------------------------- compat kernels
+
+__global__ void begin_step_kernel(b200amp_step_state *st)
+{
+    st->found_inf = 0;
+    st->inv_scale = 1.0f / st->loss_scale;
+}
+
+constexpr int COMPAT_THREADS = 256;
+constexpr int COMPAT_UNROLL = 4;
+
+// Same partition and the same order of additions as cuda/kernels/scaler.cu:39-66
+// (512 x 256 threads, quad i belongs to thread i mod 131072, squares added quad after
+// quad in fp32, butterfly over the warp, 8 warp sums through shared memory, butterfly
+// again), so partial[] carries the reference's bits. The loads of COMPAT_UNROLL quads are
+// issued together; the additions stay in order.
+__global__ void __launch_bounds__(COMPAT_THREADS)
+    unscale_norm_f32_kernel(float4 *g4, long long n4, b200amp_step_state *st, float *partial)
+{
+    __shared__ float warp_part[32];
+    const float inv = st->inv_scale;
+    const long long stride = static_cast<long long>(gridDim.x) * COMPAT_THREADS;
+    float sum = 0.0f;
+    bool bad = false;
+    long long i = static_cast<long long>(blockIdx.x) * COMPAT_THREADS + threadIdx.x;
+    for (; i + (COMPAT_UNROLL - 1) * stride < n4; i += COMPAT_UNROLL * stride)
+    {
+        float4 q[COMPAT_UNROLL];
+#pragma unroll
+        for (int u = 0; u < COMPAT_UNROLL; u++)
+        {
+            q[u] = g4[i + u * stride];
+        }
+#pragma unroll
+        for (int u = 0; u < COMPAT_UNROLL; u++)
+        {
+            float4 g = q[u];
+            g.x *= inv;
+            g.y *= inv;
+            g.z *= inv;
+            g.w *= inv;
+            g4[i + u * stride] = g;
+            bad = bad || !isfinite(g.x) || !isfinite(g.y) || !isfinite(g.z) || !isfinite(g.w);
+            sum += g.x * g.x + g.y * g.y + g.z * g.z + g.w * g.w;
+        }
+    }
+    for (; i < n4; i += stride)
+    {
+        float4 g = g4[i];
+        g.x *= inv;
+        g.y *= inv;
+        g.z *= inv;
+        g.w *= inv;
+        g4[i] = g;
+        bad = bad || !isfinite(g.x) || !isfinite(g.y) || !isfinite(g.z) || !isfinite(g.w);
+        sum += g.x * g.x + g.y * g.y + g.z * g.z + g.w * g.w;
+    }
+    if (bad)
+    {
+        st->found_inf = 1;                  // every writer stores the same value
+    }
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    sum = warp_sum_f32(sum);
+    if (lane == 0)
+    {
+        warp_part[warp] = sum;
+    }
+    __syncthreads();
+    float total = lane < COMPAT_THREADS / 32 ? warp_part[lane] : 0.0f;
+    total = warp_sum_f32(total);
+    if (threadIdx.x == 0)
+    {
+        partial[blockIdx.x] = total;
+    }
+}
+
+// 512 partials -> double, halving tree in shared memory (the fixed order of
+// cuda/kernels/scaler.cu:118-129), then the finalize on thread 0.
+__global__ void __launch_bounds__(B200AMP_NORM_BLOCKS)
+    finalize_partials_kernel(b200amp_step_state *st, const float *partial, b200amp_schedule cfg,
+                             b200amp_step_state *history, int history_len)
+{
+    __shared__ double tree[B200AMP_NORM_BLOCKS];
+    const int tid = threadIdx.x;
+    tree[tid] = static_cast<double>(partial[tid]);
+    __syncthreads();
+    for (int half = B200AMP_NORM_BLOCKS / 2; half > 0; half >>= 1)
+    {
+        if (tid < half)
+        {
+            tree[tid] += tree[tid + half];
+        }
+        __syncthreads();
+    }
+    if (tid == 0)
+    {
+        finalize_state(st, tree[0], 0, cfg, history, history_len, false);
+    }
+}
+
+__global__ void lr_probe_kernel(double *out, int step, b200amp_schedule cfg)
+{
+    *out = schedule_lr(step, cfg);
+}
+
+// ---------------------------------------------------------------- native pass 1
+
+constexpr int P1_THREADS = 256;
+constexpr int P1_WARPS = P1_THREADS / 32;
+constexpr int P1_UNROLL = 4;                    // independent 16-byte loads (and accumulators) per thread
+constexpr int P1_MAX_VBLOCKS = 148 * 32;        // virtual blocks at most: 4736
+constexpr long long P1_MIN_VEC_PER_VBLOCK = P1_THREADS * P1_UNROLL;
+
+// Workspace layout. sums comes first so a rank can all-gather its first 16 bytes.
+struct Workspace
+{
+    double sums[2];                 // out: squared norm of the range, flag as 0.0 / 1.0
+    unsigned int ticket;            // blocks finished so far; the last one resets it
+    int bad;                        // any block saw an inf/NaN; the last one resets it
+    unsigned int pad[2];
+    double partial[P1_MAX_VBLOCKS]; // one fp64 sum per virtual block
+};
+
+// How the arena is cut into virtual blocks: a function of n alone.
+struct P1Partition
+{
+    int vblocks;
+    long long vec_per_vblock;       // 16-byte vectors (8 fp16) per virtual block, the last may be short
+};
+
+__host__ __device__ inline P1Partition p1_partition(long long n8)
+{
+    P1Partition p;
+    long long per = (n8 + P1_MAX_VBLOCKS - 1) / P1_MAX_VBLOCKS;
+    if (per < P1_MIN_VEC_PER_VBLOCK)
+    {
+        per = P1_MIN_VEC_PER_VBLOCK;
+    }
+    // whole trips of the unrolled loop, so only the arena's end needs bounds checks
+    per = (per + P1_MIN_VEC_PER_VBLOCK - 1) / P1_MIN_VEC_PER_VBLOCK * P1_MIN_VEC_PER_VBLOCK;
+    p.vec_per_vblock = per;
+    p.vblocks = static_cast<int>((n8 + per - 1) / per);
+    return p;
+}
+
+// Squares of 8 unscaled gradients added to acc in element order; nonfinite bits or-ed into bad.
+__device__ __forceinline__ void accumulate_h8(const uint4 &w, float inv, float &acc, uint32_t &bad)
+{
+    bad |= half2_nonfinite_bits(w.x) | half2_nonfinite_bits(w.y) | half2_nonfinite_bits(w.z) |
+           half2_nonfinite_bits(w.w);
+    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int k = 0; k < 4; k++)
+    {
+        float2 f = half2_bits_to_float2(words[k]);
+        const float a = f.x * inv;              // exact: inv is a power of two
+        const float b = f.y * inv;
+        acc = fmaf(a, a, acc);
+        acc = fmaf(b, b, acc);
+    }
+}
+
+// FINALIZE: the last block also runs finalize_state (one GPU holds the whole arena).
+// Otherwise it only publishes {sum, flag} in the workspace (a shard of a larger arena).
+template <bool FINALIZE>
+__global__ void __launch_bounds__(P1_THREADS)
+    pass1_f16_kernel(const uint4 *__restrict__ g8, long long n8, b200amp_step_state *st, Workspace *ws,
+                     b200amp_schedule cfg, b200amp_step_state *history, int history_len)
+{
+    __shared__ double warp_part[P1_WARPS];
+    __shared__ int last_block;
+
+    const float inv = 1.0f / st->loss_scale;
+    const P1Partition part = p1_partition(n8);
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    uint32_t bad = 0;
+
+    for (int vb = blockIdx.x; vb < part.vblocks; vb += gridDim.x)
+    {
+        const long long begin = static_cast<long long>(vb) * part.vec_per_vblock;
+        long long end = begin + part.vec_per_vblock;
+        if (end > n8)
+        {
+            end = n8;
+        }
+        float acc[P1_UNROLL];
+#pragma unroll
+        for (int u = 0; u < P1_UNROLL; u++)
+        {
+            acc[u] = 0.0f;
+        }
+        long long i = begin + threadIdx.x;
+        // full trips: P1_UNROLL loads in flight per thread
+        for (; i + (P1_UNROLL - 1) * P1_THREADS < end; i += P1_UNROLL * P1_THREADS)
+        {
+            uint4 w[P1_UNROLL];
+#pragma unroll
+            for (int u = 0; u < P1_UNROLL; u++)
+            {
+                w[u] = load_h8<1>(g8 + i + u * P1_THREADS);
+            }
+#pragma unroll
+            for (int u = 0; u < P1_UNROLL; u++)
+            {
+                accumulate_h8(w[u], inv, acc[u], bad);
+            }
+        }
+        // the arena's ragged end: same slot -> same accumulator as a full trip would use
+#pragma unroll
+        for (int u = 0; u < P1_UNROLL; u++)
+        {
+            if (i + u * P1_THREADS < end)
+            {
+                uint4 w = load_h8<1>(g8 + i + u * P1_THREADS);
+                accumulate_h8(w, inv, acc[u], bad);
+            }
+        }
+        const float mine = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+        double total = warp_sum_f64(static_cast<double>(mine));
+        if (lane == 0)
+        {
+            warp_part[warp] = total;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0)
+        {
+            double block_total = 0.0;
+#pragma unroll
+            for (int w = 0; w < P1_WARPS; w++)
+            {
+                block_total += warp_part[w];
+            }
+            ws->partial[vb] = block_total;
+        }
+        __syncthreads();                        // warp_part is reused by the next virtual block
+    }
+
+    const int block_bad = __syncthreads_or(bad != 0);
+    if (threadIdx.x == 0)
+    {
+        if (block_bad)
+        {
+            atomicOr(&ws->bad, 1);
+        }
+        __threadfence();                        // partials and flag before the ticket
+        const unsigned int t = atomicAdd(&ws->ticket, 1u);
+        last_block = (t == gridDim.x - 1) ? 1 : 0;
+    }
+    __syncthreads();
+    if (!last_block)
+    {
+        return;
+    }
+    __threadfence();                            // the other blocks' partials after the ticket
+
+    // the last block: partials in a fixed order, whatever block this happens to be
+    __shared__ double tree[P1_THREADS];
+    double mine = 0.0;
+    for (int k = threadIdx.x; k < part.vblocks; k += P1_THREADS)
+    {
+        mine += __ldcg(&ws->partial[k]);
+    }
+    tree[threadIdx.x] = mine;
+    __syncthreads();
+    for (int half = P1_THREADS / 2; half > 0; half >>= 1)
+    {
+        if (threadIdx.x < half)
+        {
+            tree[threadIdx.x] += tree[threadIdx.x + half];
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0)
+    {
+        const int any_bad = __ldcg(&ws->bad);
+        ws->sums[0] = tree[0];
+        ws->sums[1] = any_bad ? 1.0 : 0.0;
+        ws->bad = 0;                            // ready for the next step (graph replays run no memset)
+        ws->ticket = 0;
+        if (FINALIZE)
+        {
+            finalize_state(st, tree[0], any_bad, cfg, history, history_len, true);
+        }
+    }
+}
+
+// Pairs {sum, flag} of every rank, added in rank order.
+__global__ void finalize_sums_kernel(b200amp_step_state *st, const double *sums, int nranks, b200amp_schedule cfg,
+                                     b200amp_step_state *history, int history_len)
+{
+    double total = 0.0;
+    int bad = 0;
+    for (int r = 0; r < nranks; r++)
+    {
+        total += sums[2 * r];
+        bad |= (sums[2 * r + 1] != 0.0) ? 1 : 0;
+    }
+    finalize_state(st, total, bad, cfg, history, history_len, true);
+}
+
+static int check_schedule(const b200amp_schedule *cfg, const b200amp_step_state *history, int history_len)
+{
+    B200AMP_REQUIRE(cfg != nullptr, "schedule is null");
+    B200AMP_REQUIRE(history == nullptr || history_len > 0, "history given with history_len %d", history_len);
+    return B200AMP_OK;
+}
+
+int launch_pass1(const void *grads16, long long n, b200amp_step_state *st, void *workspace, bool finalize,
+                 const b200amp_schedule *cfg, b200amp_step_state *history, int history_len, cudaStream_t s)
+{
+    B200AMP_REQUIRE(grads16 != nullptr && st != nullptr && workspace != nullptr, "pass 1: null pointer");
+    B200AMP_REQUIRE(n > 0 && n % 8 == 0, "pass 1: n = %lld must be a positive multiple of 8", n);
+    B200AMP_REQUIRE(aligned(grads16, 16), "pass 1: the fp16 gradient pointer must be 16-byte aligned");
+    B200AMP_REQUIRE(aligned(workspace, 16), "pass 1: the workspace must be 16-byte aligned");
+    const long long n8 = n / 8;
+    const int sms = sm_count();
+    if (sms <= 0)
+    {
+        return B200AMP_ERR_CUDA;
+    }
+    const P1Partition part = p1_partition(n8);
+    int grid = sms * tunables().pass1_blocks_per_sm;
+    if (grid > part.vblocks)
+    {
+        grid = part.vblocks;
+    }
+    b200amp_schedule c = {};
+    if (finalize)
+    {
+        int rc = check_schedule(cfg, history, history_len);
+        if (rc != B200AMP_OK)
+        {
+            return rc;
+        }
+        c = *cfg;
+        pass1_f16_kernel<true><<<grid, P1_THREADS, 0, s>>>(static_cast<const uint4 *>(grads16), n8, st,
+                                                           static_cast<Workspace *>(workspace), c, history,
+                                                           history_len);
+    }
+    else
+    {
+        pass1_f16_kernel<false><<<grid, P1_THREADS, 0, s>>>(static_cast<const uint4 *>(grads16), n8, st,
+                                                            static_cast<Workspace *>(workspace), c, nullptr, 0);
+    }
+    B200AMP_LAUNCHED();
+    return B200AMP_OK;
+}
+
+} // namespace b200amp
+
+using namespace b200amp;
+
+// ---------------------------------------------------------------- C ABI
+
+extern "C" B200AMP_API int b200amp_initial_state(float scale, b200amp_step_state *out)
+{
+    B200AMP_REQUIRE(out != nullptr, "initial_state: out is null");
+    b200amp_step_state st = {};
+    st.loss_scale = scale;
+    st.inv_scale = 1.0f / scale;
+    st.clip_coef = 1.0f;
+    st.decay = 1.0f;
+    *out = st;
+    return B200AMP_OK;
+}
+
+extern "C" B200AMP_API int b200amp_begin_step(b200amp_step_state *st, b200amp_stream s)
+{
+    B200AMP_REQUIRE(st != nullptr, "begin_step: state is null");
+    begin_step_kernel<<<1, 1, 0, as_stream(s)>>>(st);
+    B200AMP_LAUNCHED();
+    return B200AMP_OK;
+}
+
+extern "C" B200AMP_API int b200amp_unscale_and_norm_f32(float *grads, long long n, b200amp_step_state *st, float *partial,
+                                            b200amp_stream s)
+{
+    B200AMP_REQUIRE(grads != nullptr && st != nullptr && partial != nullptr, "unscale_and_norm: null pointer");
+    B200AMP_REQUIRE(n > 0 && n % 4 == 0, "unscale_and_norm: n = %lld must be a positive multiple of 4", n);
+    B200AMP_REQUIRE(aligned(grads, 16), "unscale_and_norm: grads must be 16-byte aligned");
+    unscale_norm_f32_kernel<<<B200AMP_NORM_BLOCKS, COMPAT_THREADS, 0, as_stream(s)>>>(
+        reinterpret_cast<float4 *>(grads), n / 4, st, partial);
+    B200AMP_LAUNCHED();
+    return B200AMP_OK;
+}
+
+extern "C" B200AMP_API int b200amp_finalize_step(b200amp_step_state *st, const float *partial, const b200amp_schedule *cfg,
+                                     b200amp_step_state *history, int history_len, b200amp_stream s)
+{
+    B200AMP_REQUIRE(st != nullptr && partial != nullptr, "finalize_step: null pointer");
+    int rc = check_schedule(cfg, history, history_len);
+    if (rc != B200AMP_OK)
+    {
+        return rc;
+    }
+    finalize_partials_kernel<<<1, B200AMP_NORM_BLOCKS, 0, as_stream(s)>>>(st, partial, *cfg, history, history_len);
+    B200AMP_LAUNCHED();
+    return B200AMP_OK;
+}
+
+extern "C" B200AMP_API int b200amp_lr_on_gpu(int step, const b200amp_schedule *cfg, double *out)
+{
+    B200AMP_REQUIRE(cfg != nullptr && out != nullptr, "lr_on_gpu: null pointer");
+    double *d = nullptr;
+    B200AMP_CUDA(cudaMalloc(&d, sizeof(double)));
+    lr_probe_kernel<<<1, 1>>>(d, step, *cfg);
+    count_launch();
+    cudaError_t err = cudaGetLastError();
+    if (err == cudaSuccess)
+    {
+        err = cudaMemcpy(out, d, sizeof(double), cudaMemcpyDeviceToHost);
+    }
+    cudaFree(d);
+    if (err != cudaSuccess)
+    {
+        return cuda_fail(err, "lr_on_gpu", __FILE__, __LINE__);
+    }
+    return B200AMP_OK;
+}
+
+extern "C" B200AMP_API size_t b200amp_workspace_bytes(void)
+{
+    return sizeof(Workspace);
+}
+
+extern "C" B200AMP_API int b200amp_workspace_init(void *workspace, b200amp_stream s)
+{
+    B200AMP_REQUIRE(workspace != nullptr, "workspace_init: null pointer");
+    B200AMP_CUDA(cudaMemsetAsync(workspace, 0, sizeof(Workspace), as_stream(s)));
+    return B200AMP_OK;
+}
+
+extern "C" B200AMP_API int b200amp_pass1_f16(const void *grads16, long long n, const b200amp_step_state *st, void *workspace,
+                                 b200amp_stream s)
+{
+    return launch_pass1(grads16, n, const_cast<b200amp_step_state *>(st), workspace, false, nullptr, nullptr, 0,
+                        as_stream(s));
+}
+
+extern "C" B200AMP_API int b200amp_pass1_finalize_f16(const void *grads16, long long n, b200amp_step_state *st, void *workspace,
+                                          const b200amp_schedule *cfg, b200amp_step_state *history, int history_len,
+                                          b200amp_stream s)
+{
+    return launch_pass1(grads16, n, st, workspace, true, cfg, history, history_len, as_stream(s));
+}
+
+extern "C" B200AMP_API int b200amp_finalize_sums(b200amp_step_state *st, const double *sums, int nranks,
+                                     const b200amp_schedule *cfg, b200amp_step_state *history, int history_len,
+                                     b200amp_stream s)
+{
+    B200AMP_REQUIRE(st != nullptr && sums != nullptr, "finalize_sums: null pointer");
+    B200AMP_REQUIRE(nranks > 0, "finalize_sums: nranks = %d", nranks);
+    int rc = check_schedule(cfg, history, history_len);
+    if (rc != B200AMP_OK)
+    {
+        return rc;
+    }
+    finalize_sums_kernel<<<1, 1, 0, as_stream(s)>>>(st, sums, nranks, *cfg, history, history_len);
+    B200AMP_LAUNCHED();
+    return B200AMP_OK;
+}

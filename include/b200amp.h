@@ -1,0 +1,228 @@
+/* b200amp.h: C ABI of the B200 (sm_100a) mixed-precision AdamW optimizer step.
+ *
+ * The library replaces one path of cuda-transformer: the AMP optimizer step
+ * that FastGPT::optimizer_step (cuda/gpt_fast.cu:438-450) runs every training
+ * step. Every entry point takes plain pointers, sizes and a stream, returns an
+ * int status (0 = ok) and never calls exit(): the reference's launchers print
+ * and exit(1) on a CUDA error (cuda/common.h:10-20); a caller that wants that
+ * behaviour wraps the status (compat/fast_shim.h does).
+ *
+ * Two families of entry points:
+ *
+ *   compat  (…_f32)  same arguments and in/out behaviour as the reference's
+ *                    launchers in cuda/kernels/fast.h:136-166: fp32 gradient
+ *                    arena, unscaled IN PLACE, partial[512] owned by the caller.
+ *   native  (…_f16)  the gradient arena is fp16 and read-only (2 B/param in
+ *                    pass 1, 28 B/param in pass 2); the unscale is folded into
+ *                    both passes, the finalize into the tail of pass 1. A range
+ *                    of the arena (a ZeRO-1 shard) is addressed by passing the
+ *                    shard's pointers plus its global offset.
+ *
+ * Ownership: the caller owns every device buffer, as in the reference
+ * (cuda/common.h:51-127). The ops allocate nothing; the only exceptions are
+ * b200amp_lr_on_gpu (8 bytes, as cuda/kernels/scaler.cu:100-110 does) and the
+ * graph helpers (the graph objects themselves).
+ *
+ * Streams: everything is enqueued on the stream given, without a host sync,
+ * and can be captured into a CUDA graph (changing scalars live in the step
+ * state in device memory, cuda/graph.h:4-8).
+ */
+#ifndef B200AMP_H
+#define B200AMP_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Exported with default visibility; everything else in the library is hidden. */
+#if defined(__GNUC__)
+#define B200AMP_API __attribute__((visibility("default")))
+#else
+#define B200AMP_API
+#endif
+
+/* A cudaStream_t, passed as an opaque pointer so this header needs no CUDA headers. */
+typedef void *b200amp_stream;
+
+/* ---------------------------------------------------------------- status codes */
+enum
+{
+    B200AMP_OK = 0,
+    B200AMP_ERR_ARG = 1,        /* null pointer, bad size, misaligned pointer, table too long */
+    B200AMP_ERR_CUDA = 2,       /* a CUDA runtime call or a launch failed; b200amp_last_error() has the text */
+    B200AMP_ERR_DEVICE = 3,     /* the current device is not compute capability 10.x */
+    B200AMP_ERR_LIMIT = 4       /* a size beyond a stated maximum of the entry point */
+};
+
+/* Text of the last error on the calling thread ("" if none). */
+B200AMP_API const char *b200amp_last_error(void);
+/* Library version, "major.minor.patch". */
+B200AMP_API const char *b200amp_version(void);
+/* B200AMP_OK if the current device can run the kernels (compute capability 10.x). */
+B200AMP_API int b200amp_device_check(void);
+
+/* ---------------------------------------------------------------- types
+ * Bit-compatible with the reference's structs (cuda/kernels/fast.h:104-133,
+ * 153-158): 15 x 4 bytes = 60 B, 11 x 4 bytes = 44 B, and 24 B with padding.
+ * sizeof(b200amp_step_state) is also the reference's checkpoint ABI
+ * (cuda/checkpoint.cu:102-103). */
+typedef struct b200amp_step_state
+{
+    float loss_scale;       /* S, multiplies dlogits at the start of backward */
+    float inv_scale;        /* 1 / S of THIS step */
+    int good_steps;         /* finite steps in a row since S last changed */
+    int found_inf;          /* this step's gradients held an inf or NaN: the step is skipped */
+    int skipped;            /* steps skipped so far */
+    int step;               /* steps so far, skipped ones included (drives the lr schedule) */
+    int adam_t;             /* AdamW steps taken (skipped steps do not count) */
+    float lr;               /* of this step */
+    float grad_norm;        /* of the unscaled gradients, before clipping */
+    float clip_coef;        /* min(1, clip / (norm + 1e-6)) */
+    float step_size;        /* lr / (1 - beta1^t) */
+    float bc2_sqrt;         /* sqrt(1 - beta2^t) */
+    float decay;            /* 1 - lr * weight_decay */
+    float loss;             /* written by the caller's forward pass; carried, never read here */
+    int n_valid;            /* written by the caller's forward pass; carried, never read here */
+} b200amp_step_state;
+
+typedef struct b200amp_schedule
+{
+    float lr, min_lr;
+    int warmup_steps, max_steps;
+    float beta1, beta2;
+    float weight_decay;
+    float grad_clip;
+    int growth_interval;    /* finite steps in a row before S doubles (2000 in the reference) */
+    int dynamic_scale;      /* 0: S never changes */
+    int decay_steps;        /* 0: cosine after warmup; > 0: WSD */
+} b200amp_schedule;
+
+typedef struct b200amp_tensor_info
+{
+    long long offset;       /* first element of the tensor in the arena */
+    long long count;
+    int decay;              /* 1: weight decay applies (>= 2-D weights), 0: it does not */
+} b200amp_tensor_info;
+
+#define B200AMP_NORM_BLOCKS 512     /* partial[] length of the compat path (cuda/kernels/fast.h:150) */
+#define B200AMP_MAX_TENSORS 1024    /* longest tensor table (cuda/kernels/fast.h:163) */
+
+/* ---------------------------------------------------------------- compat entry points */
+
+/* Replaces initial_state (cuda/kernels/scaler.cu:21-29). Host only: a zeroed
+ * state with loss_scale = scale, inv_scale = 1/scale, clip_coef = decay = 1. */
+B200AMP_API int b200amp_initial_state(float scale, b200amp_step_state *out);
+
+/* Replaces begin_step (cuda/kernels/scaler.cu:31-35,173-177):
+ * found_inf = 0, inv_scale = 1 / loss_scale. st is a device pointer. */
+B200AMP_API int b200amp_begin_step(b200amp_step_state *st, b200amp_stream s);
+
+/* Replaces unscale_and_norm (cuda/kernels/scaler.cu:39-66,179-184).
+ * grads[n] fp32 is multiplied by st->inv_scale in place; st->found_inf is set
+ * to 1 if any result is not finite; partial[512] receives fp32 sums of squares
+ * whose total is the squared norm. n > 0 and n % 4 == 0; grads 16-byte aligned. */
+B200AMP_API int b200amp_unscale_and_norm_f32(float *grads, long long n, b200amp_step_state *st, float *partial,
+                                 b200amp_stream s);
+
+/* Replaces finalize_step (cuda/kernels/scaler.cu:115-171,186-192): norm, clip
+ * coefficient, lr of this step, skip decision, loss-scale backoff/growth, bias
+ * corrections, history[step % history_len] = state (history may be null), step++.
+ * cfg is a HOST pointer, read before the call returns (the reference passes it by value). */
+B200AMP_API int b200amp_finalize_step(b200amp_step_state *st, const float *partial, const b200amp_schedule *cfg,
+                          b200amp_step_state *history, int history_len, b200amp_stream s);
+
+/* Replaces adamw_multi (cuda/kernels/adamw_multi.cu:20-108): one launch over the
+ * flat arena; does nothing when st->found_inf is set. grads are the UNSCALED fp32
+ * gradients. params_x (fp16, may be null) receives the rounded-to-nearest copy of
+ * the new parameters. n > 0, n % 4 == 0, every tensor offset a multiple of 4,
+ * 1 <= ntensors <= 1024; tensors and st are device pointers. */
+B200AMP_API int b200amp_adamw_multi_f32(float *params, void *params_x, const float *grads, float *m, float *v, long long n,
+                            const b200amp_tensor_info *tensors, int ntensors, const b200amp_step_state *st,
+                            float beta1, float beta2, float eps, b200amp_stream s);
+
+/* Replaces lr_on_gpu (cuda/kernels/scaler.cu:95-110): the lr of 0-based step,
+ * computed on the device in double. Synchronous; allocates and frees 8 bytes. */
+B200AMP_API int b200amp_lr_on_gpu(int step, const b200amp_schedule *cfg, double *out);
+
+/* Replaces cast_to_x of the fp16 build (cuda/kernels/fused.cu:285-292,319-323):
+ * out[i] = fp16(in[i]), round to nearest even. Used to initialise the fp16
+ * weight arena. Any n >= 0; pointers need only their natural alignment. */
+B200AMP_API int b200amp_cast_to_x(void *out_f16, const float *in, long long n, b200amp_stream s);
+
+/* ---------------------------------------------------------------- native entry points
+ * The fp16 gradient arena holds loss-scaled gradients, as the backward pass
+ * leaves them; it is never written. n % 8 == 0 and every pointer 32-byte
+ * aligned (16 for the fp16 arenas). The workspace is device memory of
+ * b200amp_workspace_bytes() bytes, zeroed once with b200amp_workspace_init();
+ * after that the kernels keep it consistent themselves (the ticket counter
+ * resets itself, so graph replays need no memset). */
+B200AMP_API size_t b200amp_workspace_bytes(void);
+B200AMP_API int b200amp_workspace_init(void *workspace, b200amp_stream s);
+
+/* Pass 1 on [grads16, grads16 + n): sum of squares of the unscaled gradients
+ * (g * 1/st->loss_scale) and the inf/NaN flag. Reads 2 B/param, writes nothing
+ * but the workspace: on return of the kernel the first two doubles of the
+ * workspace are {sum of squares, flag (0.0 or 1.0)}. The summation order depends
+ * on n only (fixed virtual grid), never on the launch, so a replay gives the
+ * same bits. No reference counterpart takes fp16 gradients; the arithmetic is
+ * that of cuda/kernels/scaler.cu:39-66 on float(fp16 gradient). */
+B200AMP_API int b200amp_pass1_f16(const void *grads16, long long n, const b200amp_step_state *st, void *workspace,
+                      b200amp_stream s);
+
+/* Finalize from nranks pairs {sum of squares, flag} laid out rank after rank
+ * (device memory, e.g. the output of an all-gather of every rank's first 16
+ * workspace bytes). Pairs are added in rank order, so every rank computes the
+ * same bits. Also sets st->inv_scale = 1/loss_scale (of this step) and
+ * st->found_inf. Otherwise cuda/kernels/scaler.cu:131-170. */
+B200AMP_API int b200amp_finalize_sums(b200amp_step_state *st, const double *sums, int nranks, const b200amp_schedule *cfg,
+                          b200amp_step_state *history, int history_len, b200amp_stream s);
+
+/* Pass 1 and the finalize in ONE launch (the last block to finish runs the
+ * finalize), for an arena held by one GPU. */
+B200AMP_API int b200amp_pass1_finalize_f16(const void *grads16, long long n, b200amp_step_state *st, void *workspace,
+                               const b200amp_schedule *cfg, b200amp_step_state *history, int history_len,
+                               b200amp_stream s);
+
+/* Pass 2 on a range of the arena: clip, AdamW on master/m/v (fp32, updated in
+ * place), fp16 weight cast. Reads 14 B/param, writes 14 B/param. All array
+ * pointers address the FIRST ELEMENT OF THE RANGE; arena_offset is that
+ * element's index in the whole arena (0 for an unsharded arena) and is what
+ * the tensor table is searched with. weights16 may be null. Does nothing when
+ * st->found_inf is set. Arithmetic per element: cuda/kernels/adamw_multi.cu:20-29,75-89
+ * with g = float(fp16 gradient) * st->inv_scale. */
+B200AMP_API int b200amp_pass2_f16(float *master, float *m, float *v, const void *grads16, void *weights16, long long n,
+                      long long arena_offset, const b200amp_tensor_info *tensors, int ntensors,
+                      const b200amp_step_state *st, float beta1, float beta2, float eps, b200amp_stream s);
+
+/* The whole step for an arena held by one GPU: b200amp_pass1_finalize_f16 then
+ * b200amp_pass2_f16 (two launches). */
+B200AMP_API int b200amp_step_f16(float *master, float *m, float *v, const void *grads16, void *weights16, long long n,
+                     const b200amp_tensor_info *tensors, int ntensors, b200amp_step_state *st, void *workspace,
+                     const b200amp_schedule *cfg, b200amp_step_state *history, int history_len,
+                     float beta1, float beta2, float eps, b200amp_stream s);
+
+/* ---------------------------------------------------------------- CUDA-graph helpers
+ * Replace CudaGraph::{capture,launch} and its destructor (cuda/graph.h:14-30,
+ * cuda/graph.cu:17-41): begin puts s in thread-local capture mode, the caller
+ * enqueues the step, end instantiates. */
+typedef struct b200amp_graph b200amp_graph;
+B200AMP_API int b200amp_graph_begin_capture(b200amp_stream s);
+B200AMP_API int b200amp_graph_end_capture(b200amp_stream s, b200amp_graph **out);
+B200AMP_API int b200amp_graph_launch(b200amp_graph *g, b200amp_stream s);
+B200AMP_API int b200amp_graph_destroy(b200amp_graph *g);
+
+/* ---------------------------------------------------------------- tuning hooks
+ * Launch-shape knobs for measurement (blocks per SM, variant); not part of the
+ * reference's surface. Unknown keys return B200AMP_ERR_ARG. Results never depend on them. */
+B200AMP_API int b200amp_tune_set(const char *key, int value);
+B200AMP_API int b200amp_tune_get(const char *key, int *value);
+/* Kernel launches enqueued by this library on the calling process so far. */
+B200AMP_API long long b200amp_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* B200AMP_H */
