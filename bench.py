@@ -1,0 +1,405 @@
+#!/usr/bin/env python
+"""Benchmark of the AMP AdamW optimizer step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One "step" is one pass of the hot path over the whole parameter arena: pass 1 (unscale +
+inf/NaN flag + squared-norm partials + finalize) and pass 2 (clip + AdamW on fp32
+master/m/v + fp16 weight cast) on loss-scaled fp16 gradients. The default workload is the
+1.3 B-parameter arena (L24 H16 C2048 Vp50304 n_ctx2048, 1,315,819,520 parameters, 292
+tensors); at N > 1 the same arena is sharded ZeRO-1 style over the ranks (strong scaling):
+reduce-scatter of fp16 gradients, the two passes on the shard, a 16-byte all-gather for the
+norm and flag, and an all-gather of the fp16 weights.
+
+Prints ONE JSON line (rank 0). `value` is Gparams/s with every input resident in HBM;
+`e2e` is the same metric when each step first copies its fp16 gradients from pinned host
+memory and ends with a device-to-host read of the 60-byte step state. `roofline` is the
+dominant kernel (pass 2, 28 algorithmic bytes per parameter) against the measured HBM copy
+bandwidth. `cpu_baseline` / `--impl reference` time the reference's PyTorch CPU path
+(torch AdamW + GradScaler + clip_grad_norm_) on the host cores, on a bounded sample of the
+same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+if REPO not in sys.path:
+    sys.path.insert(0, REPO)
+
+METRIC = "amp_adamw_step_throughput"
+UNIT = "Gparams/s"
+BYTES_PASS1 = 2            # per parameter: read the fp16 gradient
+BYTES_PASS2 = 28           # read g16 2 + master 4 + m 4 + v 4; write master 4 + m 4 + v 4 + fp16 weight 2
+BYTES_STEP = BYTES_PASS1 + BYTES_PASS2
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+NVLINK_MEASURED_GBS = 770.0     # per direction per GPU, measured peer copy on this pool
+
+
+def measured_hbm_peak():
+    path = os.path.join(REPO, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+# ---------------------------------------------------------------------------- clocks
+
+class ClockSampler:
+    """nvidia-smi in the background during the timed region (read-only queries)."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_indices):
+        self.gpus = set(int(g) for g in gpu_indices)
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(prefix="clocks_", suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, reasons, smax = [], set(), None
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 8 or not f[0].isdigit() or int(f[0]) not in self.gpus:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    smax = float(f[2])
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                     f[4:8]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            # "under load": the upper half of the samples (idle samples before/after the region drop out)
+            sm.sort()
+            out["sm_mhz"] = statistics.median(sm[len(sm) // 2:])
+            out["samples"] = len(sm)
+        out["sm_max_mhz"] = smax
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+# ---------------------------------------------------------------------------- workloads
+
+def workload_slots(name: str):
+    from cuda_transformer_b200.layout import CONFIGS, param_layout
+    return param_layout(CONFIGS[name])
+
+
+def cpu_sample_shapes(name: str):
+    """A bounded sample of the workload for the CPU path: the first tensors of the arena after
+    the token embedding (wpe, two whole layers) plus the final LayerNorm, with their real shapes."""
+    slots = workload_slots(name)
+    per_layer = 12
+    keep = slots[1:2 + 2 * per_layer] + slots[-2:]
+    return [s.shape for s in keep], "wpe + layers 0-1 + ln_f of the %s arena" % name
+
+
+def run_cpu_reference(workload: str, steps: int, warmup: int) -> dict:
+    """The reference's PyTorch CPU path (reference/train.py:147-153 order) on the host cores."""
+    from oracle.torch_ref import time_cpu_step
+    shapes, what = cpu_sample_shapes(workload)
+    r = time_cpu_step(shapes, steps=max(1, steps), warmup=max(1, warmup), loss_scale=32768.0)
+    gps = r["params"] / r["seconds_per_step"] / 1e9
+    return {"value": gps, "unit": UNIT, "cores": r["threads"], "kind": "port",
+            "sample": f"{what}: {r['params']:,} params/step, median of {max(1, steps)} steps; "
+                      "torch.optim.AdamW(foreach=False) + GradScaler('cpu') + clip_grad_norm_, "
+                      f"host has {os.cpu_count()} logical cores",
+            "ms_per_step": r["seconds_per_step"] * 1e3, "params": r["params"]}
+
+
+# ---------------------------------------------------------------------------- GPU arm
+
+def fill_normal_(t, std, seed, chunk=1 << 27):
+    """t ~ N(0, std) from a seeded device generator, in chunks (no arena-sized temporary)."""
+    import torch
+    gen = torch.Generator(device=t.device).manual_seed(seed)
+    for at in range(0, t.numel(), chunk):
+        sl = t[at:at + chunk]
+        sl.copy_(torch.randn(sl.numel(), generator=gen, device=t.device, dtype=torch.float32) * std)
+
+
+def run_gpu(args) -> dict:
+    import torch
+    import torch.distributed as dist
+    from cuda_transformer_b200 import _lib, amp
+    from cuda_transformer_b200.layout import padded
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch N > 1 with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    lib = _lib.load()
+    _lib.check(lib.b200amp_device_check())
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    slots = workload_slots(args.workload)
+    n_params = slots[-1].offset + slots[-1].count
+    n = padded(n_params)
+    loss_scale = 32768.0
+    cfg = amp.make_schedule(lr=6e-4, min_lr=6e-4, beta1=0.9, beta2=0.95, weight_decay=0.1, grad_clip=1.0,
+                            growth_interval=2000, dynamic_scale=1)
+
+    if world == 1:
+        opt = amp.AmpOptimizer(slots, cfg, eps=1e-8, loss_scale=loss_scale, device=dev)
+        fill_normal_(opt.master[:n_params], 0.02, seed=0)
+        amp.cast_to_x(opt.weights16, opt.master, n)
+        step_fn = opt.optimizer_step
+    else:
+        opt = amp.ShardedAmpOptimizer(slots, cfg, eps=1e-8, loss_scale=loss_scale, device=dev)
+        # the same master values as the 1-GPU run would hold in this slice would need the whole
+        # stream; a per-rank seed gives the same distribution, which is all the timing needs
+        fill_normal_(opt.master, 0.02, seed=100 + rank)
+        opt.weights16.zero_()
+        amp.cast_to_x(opt.weights16[opt.begin:opt.end], opt.master, opt.n_local)
+        opt.all_gather_weights()
+        step_fn = opt.optimizer_step
+
+    # fp16 gradients = N(0, 1e-3) * loss_scale, generated on the device (rank r: seed r + 1)
+    def fill_grads(seed):
+        gen = torch.Generator(device=dev).manual_seed(seed)
+        chunk = 1 << 27
+        for at in range(0, n_params, chunk):
+            m_ = min(chunk, n_params - at)
+            opt.grads16[at:at + m_].copy_(
+                (torch.randn(m_, generator=gen, device=dev, dtype=torch.float32) * (1e-3 * loss_scale)).half())
+
+    # m and v pre-warmed by 5 seeded steps of the implementation itself (untimed)
+    for k in range(5):
+        fill_grads(1000 * (k + 1) + rank + 1)
+        step_fn()
+    fill_grads(rank + 1)
+    torch.cuda.synchronize()
+    st = opt.read_state()
+    if st.skipped != 0 or st.adam_t != 5:
+        raise SystemExit(f"pre-warm went wrong: {st.as_dict()}")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ------------------------------------------------------------------ device-resident timing
+    for _ in range(args.warmup):
+        step_fn()
+    barrier()
+    sampler = ClockSampler(range(world))
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    launches_before = lib.b200amp_launch_count()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(7)] for _ in range(args.steps)]
+    t_begin = torch.cuda.Event(enable_timing=True)
+    t_end = torch.cuda.Event(enable_timing=True)
+    t_begin.record()
+    if world == 1:
+        for k in range(args.steps):
+            ev[k][0].record()
+            amp.pass1_finalize_f16(opt.grads16, opt.n, opt.state, opt.workspace, opt.sched, opt.history,
+                                   opt.history_len)
+            ev[k][1].record()
+            amp.pass2_f16(opt.master, opt.m, opt.v, opt.grads16, opt.weights16, opt.n, 0, opt.tensors,
+                          opt.ntensors, opt.state, opt.beta1, opt.beta2, opt.eps)
+            ev[k][2].record()
+    else:
+        for k in range(args.steps):
+            ev[k][0].record()
+            opt.reduce_scatter_grads()
+            ev[k][1].record()
+            opt._pass1()
+            ev[k][2].record()
+            opt.gather_sums()
+            opt._finalize()
+            ev[k][3].record()
+            opt._pass2()
+            ev[k][4].record()
+            opt.all_gather_weights()
+            ev[k][5].record()
+    t_end.record()
+    barrier()
+    launches = lib.b200amp_launch_count() - launches_before
+    total_ms = max_over_ranks(t_begin.elapsed_time(t_end))
+    if rank == 0:
+        time.sleep(0.2)
+        clocks = sampler.stop()
+    ms_per_step = total_ms / args.steps
+
+    def avg(i, j):
+        return sum(ev[k][i].elapsed_time(ev[k][j]) for k in range(args.steps)) / args.steps
+
+    phases = {}
+    if world == 1:
+        pass1_ms, pass2_ms = avg(0, 1), avg(1, 2)
+        n_local = n
+    else:
+        phases = {"reduce_scatter_ms": max_over_ranks(avg(0, 1)), "pass1_ms": max_over_ranks(avg(1, 2)),
+                  "norm_gather_finalize_ms": max_over_ranks(avg(2, 3)), "pass2_ms": max_over_ranks(avg(3, 4)),
+                  "all_gather_ms": max_over_ranks(avg(4, 5))}
+        pass1_ms, pass2_ms = phases["pass1_ms"], phases["pass2_ms"]
+        n_local = opt.n_local
+        coll_bytes = (world - 1) / world * 2 * n            # per GPU per direction, each collective
+        phases["reduce_scatter_gbs"] = coll_bytes / (phases["reduce_scatter_ms"] * 1e-3) / 1e9
+        phases["all_gather_gbs"] = coll_bytes / (phases["all_gather_ms"] * 1e-3) / 1e9
+        phases["nvlink_peak_gbs"] = NVLINK_MEASURED_GBS
+    st = opt.read_state()
+    if st.skipped != 0:
+        raise SystemExit("a timed step was skipped: the timing would count 2 B/param steps")
+
+    # ------------------------------------------------------------------ end to end: host gradients in, state out
+    e2e_steps = max(3, min(args.steps, 10))
+    host_grads = torch.empty(n, dtype=torch.float16, pin_memory=True)
+    host_grads.copy_(opt.grads16)
+    host_state = torch.empty(opt.state.numel(), dtype=torch.uint8, pin_memory=True)
+    torch.cuda.synchronize()
+
+    def e2e_step():
+        opt.grads16.copy_(host_grads, non_blocking=True)
+        step_fn()
+        host_state.copy_(opt.state, non_blocking=True)
+        torch.cuda.current_stream().synchronize()       # the caller reads the state: a real host sync
+
+    e2e_step()
+    barrier()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
+    launches += 0       # e2e launches are outside the timed region that `value` reports
+
+    if world > 1:
+        dist.barrier()
+
+    peak, peak_kind = measured_hbm_peak()
+    pass2_gbs = BYTES_PASS2 * n_local / (pass2_ms * 1e-3) / 1e9
+    pass1_gbs = BYTES_PASS1 * n_local / (pass1_ms * 1e-3) / 1e9
+    value = n_params / (ms_per_step * 1e-3) / 1e9
+    hbm_gbs_step = BYTES_STEP * n_local / ((pass1_ms + pass2_ms) * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {n_params:,} params, {len(slots)} tensors, fp16 grads "
+                               f"N(0,1e-3)*{int(loss_scale)}, fp32 master/m/v, m and v pre-warmed by 5 steps, "
+                               "AdamW lr 6e-4 betas (0.9,0.95) eps 1e-8 wd 0.1, clip 1.0",
+                   "params": n_params, "arena": n, "parallelism": "single" if world == 1 else f"zero1-dp{world}",
+                   "l2": "arenas are far larger than the 126 MB L2 (no flush needed between steps)"},
+        "hbm_gbs": hbm_gbs_step, "hbm_frac_of_nominal_8tbs": hbm_gbs_step / NOMINAL_HBM_GBS,
+        "hbm_frac_of_measured": hbm_gbs_step / peak,
+        "kernels_ms": {"pass1_finalize": pass1_ms, "pass2": pass2_ms},
+        "roofline": {"bound": "hbm", "kernel": "pass2_f16_kernel", "achieved": pass2_gbs, "peak": peak,
+                     "peak_kind": f"{peak_kind} copy bandwidth", "unit": "GB/s", "frac": pass2_gbs / peak,
+                     "traffic": None, "algorithmic_bytes_per_launch": BYTES_PASS2 * n_local,
+                     "pass1_achieved": pass1_gbs, "pass1_frac": pass1_gbs / peak},
+        "e2e": {"value": n_params / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": 2 * n, "d2h_bytes_per_step": int(opt.state.numel()), "steps": e2e_steps},
+        "gpu_launches": int(launches),
+        "clocks": clocks if rank == 0 else None,
+        "state": {k: v for k, v in st.as_dict().items() if k in ("step", "adam_t", "skipped", "loss_scale",
+                                                                  "grad_norm", "clip_coef")},
+    }
+    if phases:
+        line["phases"] = phases
+    traffic_path = os.path.join(REPO, "profiles", "pass2_traffic.json")
+    if os.path.exists(traffic_path):
+        try:
+            per_param = float(json.load(open(traffic_path))["dram_bytes_per_param"])
+            line["roofline"]["traffic"] = per_param * n_local
+            line["roofline"]["traffic_source"] = "profiles/pass2_traffic.json (ncu, scaled by parameters)"
+        except Exception:
+            pass
+    if world > 1:
+        dist.destroy_process_group()
+    return line if rank == 0 else None
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", default="1.3b", choices=["debug", "readme", "gpt2-small", "1.3b"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        slots = workload_slots(args.workload)
+        n_params = slots[-1].offset + slots[-1].count
+        r = run_cpu_reference(args.workload, steps=args.steps, warmup=max(1, args.warmup))
+        line = {"impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic",
+                "config": {"workload": f"{args.workload}: {n_params:,} params (timed on a bounded sample, see "
+                                       "cpu_baseline.sample)", "params": n_params},
+                "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+                "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line), flush=True)
+        return
+
+    line = run_gpu(args)
+    if line is None:
+        return
+    if args.gpus == 1 and not args.no_cpu_baseline:
+        r = run_cpu_reference(args.workload, steps=5, warmup=1)
+        line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,104 @@
+"""CPU-only checks of the boundary: the shared library loads, exports every symbol the header
+declares, the host-only entry points behave, and the arena layout has the reference's sizes.
+No kernel is launched here."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from cuda_transformer_b200 import _lib, build
+from cuda_transformer_b200.layout import CONFIGS, num_params, padded, param_layout, shard_range, tensor_table
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(REPO, "include", "b200amp.h")).read()
+    return sorted(set(re.findall(r"B200AMP_API[^;(]*?\b(b200amp_\w+)\s*\(", text)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    build.build()
+    return _lib.load()
+
+
+def test_library_exports_every_declared_symbol(lib):
+    names = declared_symbols()
+    assert len(names) >= 24
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared in include/b200amp.h but not exported"
+    assert sorted(_lib.PROTOTYPES) == names, "the ctypes prototypes and the header disagree"
+
+
+def test_struct_layouts_are_the_reference_abi():
+    assert C.sizeof(_lib.StepState) == 60       # cuda/kernels/fast.h:104-121; checkpoint ABI, cuda/checkpoint.cu:102-103
+    assert C.sizeof(_lib.ScheduleConfig) == 44  # cuda/kernels/fast.h:123-133
+    assert C.sizeof(_lib.TensorInfo) == 24      # cuda/kernels/fast.h:153-158
+    assert _lib.StepState.loss_scale.offset == 0 and _lib.StepState.found_inf.offset == 12
+    assert _lib.StepState.adam_t.offset == 24 and _lib.StepState.n_valid.offset == 56
+    assert _lib.TensorInfo.decay.offset == 16
+
+
+def test_host_only_entry_points(lib):
+    assert re.fullmatch(r"\d+\.\d+\.\d+", lib.b200amp_version().decode())
+    st = _lib.StepState()
+    assert lib.b200amp_initial_state(65536.0, C.byref(st)) == _lib.OK
+    assert st.loss_scale == 65536.0 and st.inv_scale == 1.0 / 65536.0
+    assert st.clip_coef == 1.0 and st.decay == 1.0
+    assert (st.good_steps, st.found_inf, st.skipped, st.step, st.adam_t, st.n_valid) == (0,) * 6
+    assert lib.b200amp_initial_state(1.0, None) == _lib.ERR_ARG
+    assert b"null" in lib.b200amp_last_error()
+    assert lib.b200amp_workspace_bytes() >= 16 + 8 * 148 * 32
+
+
+def test_tuning_knobs_round_trip(lib):
+    v = C.c_int()
+    assert lib.b200amp_tune_get(b"pass2_blocks_per_sm", C.byref(v)) == _lib.OK
+    old = v.value
+    assert lib.b200amp_tune_set(b"pass2_blocks_per_sm", 6) == _lib.OK
+    assert lib.b200amp_tune_get(b"pass2_blocks_per_sm", C.byref(v)) == _lib.OK and v.value == 6
+    assert lib.b200amp_tune_set(b"pass2_blocks_per_sm", old) == _lib.OK
+    assert lib.b200amp_tune_set(b"pass2_blocks_per_sm", 0) == _lib.ERR_ARG
+    assert lib.b200amp_tune_set(b"no_such_knob", 1) == _lib.ERR_ARG
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(build, "LIB_PATH", str(tmp_path / "absent.so"))
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        _lib.load()
+
+
+@pytest.mark.parametrize("name,n,n_pad,ntensors", [
+    ("debug", 370_432, 370_688, 28),
+    ("readme", 12_343_296, 12_343_296, 76),
+    ("gpt2-small", 124_475_904, 124_476_416, 148),
+    ("1.3b", 1_315_819_520, 1_315_819_520, 292),
+])
+def test_arena_layout_sizes(name, n, n_pad, ntensors):
+    """n = Vp*C + n_ctx*C + L*(12C^2 + 13C) + 2C (cuda/gpt.cu:82-101)."""
+    cfg = CONFIGS[name]
+    slots = param_layout(cfg)
+    C_ = cfg.C
+    assert num_params(slots) == n == cfg.Vp * C_ + cfg.n_ctx * C_ + cfg.L * (12 * C_ * C_ + 13 * C_) + 2 * C_
+    assert padded(n) == n_pad and len(slots) == ntensors <= 1024
+    at = 0
+    for s in slots:
+        assert s.offset == at and s.offset % 8 == 0 and s.count % 8 == 0   # cuda/gpt_fast.cu:111
+        at += s.count
+    table = tensor_table(slots)
+    assert [d for _, _, d in table[:4]] == [1, 1, 0, 0]      # wte, wpe decay; ln1.w, ln1.b do not
+    assert sum(d for _, _, d in table) == 2 + 4 * cfg.L
+
+
+def test_shard_ranges_tile_the_arena():
+    n = padded(124_475_904)
+    for world in (1, 2, 4, 8):
+        at = 0
+        for r in range(world):
+            b, e = shard_range(n, r, world)
+            assert b == at and (e - b) % 128 == 0
+            at = e
+        assert at == n

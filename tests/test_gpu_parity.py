@@ -1,0 +1,560 @@
+"""Parity of the CUDA path with the oracle, the golden vectors and (when built) the
+reference's own CUDA kernels. Every call goes through the C ABI of libb200amp.so."""
+import ctypes as C
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+from inputs import GradStream, inject
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def G():
+    import gpu_helpers
+    from cuda_transformer_b200 import _lib
+    _lib.check(_lib.load().b200amp_device_check())
+    return gpu_helpers
+
+
+@pytest.fixture(scope="module")
+def O():
+    from oracle import ref_step
+    ref_step.load()
+    return ref_step
+
+
+def sched(amp_or_oracle, **kw):
+    return amp_or_oracle.make_schedule(**kw)
+
+
+def compare_arrays(gpu, oracle, tol=H.STATE_TOL):
+    gm, gmm, gv, gw = gpu.host()
+    assert H.rel_err(oracle.master, gm) <= tol
+    assert H.rel_err(oracle.m, gmm) <= tol
+    assert H.rel_err(oracle.v, gv) <= tol
+    assert H.half_ulp_distance(oracle.weights16, gw) <= 1
+    # the fp16 copy is exactly fp16(master) (cuda/tests/test_fast.cu:255-267)
+    assert np.array_equal(gm.astype(np.float16).view(np.uint16), gw)
+
+
+# ---------------------------------------------------------------- debug model (config 0 sizes)
+
+def test_compat_fp32_10_steps_match_reference_optimizer(G, O):
+    """Config 0: the reference's entry points, fp32 gradients, against the golden vectors the
+    reference's PyTorch path produced and against the oracle."""
+    from cuda_transformer_b200 import amp
+    meta = H.golden_meta()
+    gold = H.golden("debug_fp32_10steps.npz")
+    slots = H.debug_slots()
+    kw = dict(lr=meta["lr"], min_lr=meta["lr"], beta1=meta["beta1"], beta2=meta["beta2"],
+              weight_decay=meta["weight_decay"], grad_clip=meta["grad_clip"], dynamic_scale=0)
+    table = H.table_of(slots)
+    gpu = G.GpuStep(H.debug_init(), table, sched(amp, **kw), eps=meta["eps"], loss_scale=1.0)
+    ora = O.OracleStep(H.debug_init(), table, sched(O, **kw), eps=meta["eps"], loss_scale=1.0, contract=1)
+    stream = GradStream(H.debug_shapes(), seed=1)
+    stride = meta["stride"]
+    for k in range(10):
+        flat = H.flat_np(stream.next_fp32())
+        g_dev = gpu.step_f32(flat)
+        g_ora = ora.step_f32(flat)
+        assert np.array_equal(g_dev.cpu().numpy(), g_ora), "in-place unscale differs"
+        st = gpu.read_state()
+        G.assert_states_equal(st, ora.state)
+        assert abs(st.grad_norm - gold["norms"][k]) <= 1e-5 * gold["norms"][k]
+        if k in (0, 9):
+            gm, gmm, gv, _ = gpu.host()
+            tag = f"step{k + 1}"
+            for what, arr in (("p", gm), ("m", gmm), ("v", gv)):
+                assert H.rel_err(gold[f"{tag}_{what}"], arr[::stride]) <= H.STATE_TOL, (tag, what)
+    compare_arrays(gpu, ora)
+    st = gpu.read_state()
+    assert st.step == 10 and st.adam_t == 10 and st.skipped == 0 and st.loss_scale == 1.0
+
+
+def test_native_amp_100_steps_trajectory_matches_reference_scaler(G, O):
+    """fp16 gradient arena, inf at steps 3/17/40, NaN at 55, growth every 8 clean steps: skip
+    decisions, loss scale, adam_t and the growth counter bit-exact against torch's GradScaler
+    (golden), state arrays against golden and oracle."""
+    from cuda_transformer_b200 import amp
+    meta = H.golden_meta()
+    a = meta["amp"]
+    gold = H.golden("debug_amp_100steps.npz")
+    slots = H.debug_slots()
+    kw = dict(lr=meta["lr"], min_lr=meta["lr"], beta1=meta["beta1"], beta2=meta["beta2"],
+              weight_decay=meta["weight_decay"], grad_clip=a["grad_clip"], growth_interval=a["growth_interval"],
+              dynamic_scale=1)
+    n = slots[-1].offset + slots[-1].count
+    n_pad = (n + 7) // 8 * 8
+    table = H.table_of(slots)
+    init = np.zeros(n_pad, dtype=np.float32)
+    init[:n] = H.debug_init()
+    gpu = G.GpuStep(init, table, sched(amp, **kw), eps=meta["eps"], loss_scale=a["loss_scale"])
+    ora = O.OracleStep(init, table, sched(O, **kw), eps=meta["eps"], loss_scale=a["loss_scale"], contract=1)
+    stream = GradStream(H.debug_shapes(), seed=1)
+    traj = a["trajectory"]
+    for k in range(a["steps"]):
+        scale = gpu.read_state().loss_scale
+        grads = stream.next_fp16_scaled(scale)
+        inj = a["injections"].get(str(k))
+        if inj:
+            inject(grads, inj["tensor"], inj["elements"], float(inj["value"]))
+        bits = np.zeros(n_pad, dtype=np.uint16)
+        bits[:n] = H.f16_bits(torch.cat([g.reshape(-1) for g in grads]))
+        before = gpu.host() if traj["found_inf"][k] else None
+        gpu.set_grads16(bits)
+        gpu.step_f16()
+        ora.step_f16(bits)
+        st = gpu.read_state()
+        assert st.loss_scale == traj["scale_after"][k], k
+        assert st.found_inf == traj["found_inf"][k], k
+        assert st.adam_t == traj["adam_t"][k], k
+        assert st.good_steps == traj["growth_tracker"][k], k
+        assert st.step == k + 1
+        G.assert_states_equal(st, ora.state)
+        if before is not None:
+            after = gpu.host()
+            assert all(np.array_equal(x, y) for x, y in zip(before, after)), "a skipped step moved state"
+        else:
+            assert abs(st.grad_norm - traj["norm"][k]) <= 1e-6 * traj["norm"][k]
+    assert gpu.read_state().skipped == 4
+    compare_arrays(gpu, ora)
+    gm, gmm, gv, gw = gpu.host()
+    stride = meta["stride"]
+    for what, arr in (("p", gm[:n]), ("m", gmm[:n]), ("v", gv[:n])):
+        assert H.rel_err(gold[what], arr[::stride]) <= H.STATE_TOL, what
+    assert H.half_ulp_distance(gold["w16"], gw[:n][::stride]) <= 1
+    # the history ring holds every finished step (cuda/kernels/scaler.cu:165-168)
+    for k in (0, 3, 55, 99):
+        h = G.read_struct(gpu.history, k)
+        assert h.step == k and h.found_inf == traj["found_inf"][k]
+
+
+# ---------------------------------------------------------------- README model (configs 1 and 2)
+
+def _readme_run(G, O, steps, injections, growth_interval, check_every):
+    from cuda_transformer_b200 import amp
+    from cuda_transformer_b200.layout import CONFIGS, param_layout
+    slots = param_layout(CONFIGS["readme"])
+    n = slots[-1].offset + slots[-1].count
+    assert n == 12_343_296
+    shapes = [s.shape for s in slots]
+    table = H.table_of(slots)
+    gen = torch.Generator().manual_seed(0)
+    init = (torch.randn(n, generator=gen) * 0.02).numpy()
+    kw = dict(lr=6e-4, min_lr=6e-4, beta1=0.9, beta2=0.95, weight_decay=0.1, grad_clip=1.0,
+              growth_interval=growth_interval, dynamic_scale=1)
+    gpu = G.GpuStep(init, table, sched(amp, **kw), loss_scale=65536.0)
+    ora = O.OracleStep(init, table, sched(O, **kw), loss_scale=65536.0, contract=1)
+    stream = GradStream(shapes, seed=1)
+    scales = []
+    for k in range(steps):
+        grads = stream.next_fp16_scaled(ora.state.loss_scale)
+        if k in injections:
+            t, idx, val = injections[k]
+            inject(grads, t, idx, val)
+        bits = H.f16_bits(torch.cat([g.reshape(-1) for g in grads]))
+        gpu.set_grads16(bits)
+        gpu.step_f16()
+        ora.step_f16(bits)
+        st = gpu.read_state()
+        G.assert_states_equal(st, ora.state)
+        scales.append(st.loss_scale)
+        if (k + 1) % check_every == 0 or k in injections:
+            compare_arrays(gpu, ora)
+    compare_arrays(gpu, ora)
+    return gpu.read_state(), scales, ora
+
+
+def test_readme_model_amp_steps_match_oracle(G, O):
+    """Config 1 (12.3 M parameters, 76 tensors, clip active: norm 3.5 -> coef 0.285), with growth
+    every 8 steps so the scale moves too."""
+    st, scales, ora = _readme_run(G, O, steps=24, injections={}, growth_interval=8, check_every=8)
+    assert st.adam_t == 24 and st.skipped == 0
+    assert scales[7] == 131072.0 and scales[15] == 262144.0 and scales[23] == 524288.0
+    assert 0.28 < ora.state.clip_coef < 0.29
+
+
+def test_readme_model_overflow_trajectory(G, O):
+    """Config 2: +inf into 0.1 % of one tensor at steps 3, 17, 40 and one NaN at step 55; 100 steps."""
+    from cuda_transformer_b200.layout import CONFIGS, param_layout
+    slots = param_layout(CONFIGS["readme"])
+    pick = torch.Generator().manual_seed(2)
+    injections = {}
+    for step, val in ((3, float("inf")), (17, float("inf")), (40, float("inf")), (55, float("nan"))):
+        t = int(torch.randint(len(slots), (1,), generator=pick))
+        if math.isinf(val):
+            k = max(1, slots[t].count // 1000)
+            idx = torch.randperm(slots[t].count, generator=pick)[:k].tolist()
+        else:
+            idx = [int(torch.randint(slots[t].count, (1,), generator=pick))]
+        injections[step] = (t, idx, val)
+    st, scales, _ = _readme_run(G, O, steps=100, injections=injections, growth_interval=2000, check_every=50)
+    assert st.skipped == 4 and st.adam_t == 96 and st.step == 100
+    expect = 65536.0
+    for k in range(100):
+        if k in injections:
+            expect *= 0.5
+        assert scales[k] == expect, k
+    assert scales[-1] == 4096.0
+
+
+# ---------------------------------------------------------------- edge cases
+
+@pytest.mark.parametrize("n", [8, 64, 2048, 8192 + 8, (1 << 20) + 24])
+def test_small_and_ragged_sizes(G, O, n):
+    from cuda_transformer_b200 import amp
+    rng = np.random.default_rng(n)
+    init = (rng.standard_normal(n) * 0.02).astype(np.float32)
+    table = [(0, n, 1)]
+    kw = dict(grad_clip=1.0)
+    gpu = G.GpuStep(init, table, sched(amp, **kw), loss_scale=1024.0)
+    ora = O.OracleStep(init, table, sched(O, **kw), loss_scale=1024.0)
+    for _ in range(3):
+        bits = (rng.standard_normal(n) * 1e-2 * 1024.0).astype(np.float16).view(np.uint16)
+        gpu.set_grads16(bits)
+        gpu.step_f16()
+        ora.step_f16(bits)
+        G.assert_states_equal(gpu.read_state(), ora.state)
+    compare_arrays(gpu, ora)
+
+
+def test_1024_tensors_and_boundaries_inside_a_group(G, O):
+    """The longest table the ABI allows; tensor edges at multiples of 4 that are not multiples of
+    8, so a decayed and an undecayed tensor share one 8-element group."""
+    from cuda_transformer_b200 import amp
+    rng = np.random.default_rng(7)
+    counts = rng.choice([4, 12, 20, 36, 260, 1028], size=1024)
+    table, at = [], 0
+    for i, c in enumerate(counts):
+        table.append((at, int(c), int(i % 2)))
+        at += int(c)
+    n = (at + 7) // 8 * 8
+    init = (rng.standard_normal(n) * 0.5).astype(np.float32)
+    kw = dict(weight_decay=0.5, lr=1e-2, min_lr=1e-2)       # a decay large enough that a wrong flag shows
+    gpu = G.GpuStep(init, table, sched(amp, **kw), loss_scale=256.0)
+    ora = O.OracleStep(init, table, sched(O, **kw), loss_scale=256.0)
+    for _ in range(2):
+        bits = (rng.standard_normal(n) * 1e-3 * 256.0).astype(np.float16).view(np.uint16)
+        gpu.set_grads16(bits)
+        gpu.step_f16()
+        ora.step_f16(bits)
+    compare_arrays(gpu, ora)
+    # and the compat kernel, whose granularity is 4
+    gpu2 = G.GpuStep(init, table, sched(amp, **kw), loss_scale=256.0)
+    ora2 = O.OracleStep(init, table, sched(O, **kw), loss_scale=256.0)
+    g = (rng.standard_normal(n) * 1e-3 * 256.0).astype(np.float32)
+    gpu2.step_f32(g)
+    ora2.step_f32(g)
+    compare_arrays(gpu2, ora2)
+
+
+def test_zero_gradients_are_not_an_overflow(G, O):
+    """An empty batch: grad_norm == 0.0 and the step is taken (cuda/tests/test_fast.cu:459-471)."""
+    from cuda_transformer_b200 import amp
+    n = 4096
+    init = np.full(n, 0.25, dtype=np.float32)
+    gpu = G.GpuStep(init, [(0, n, 1)], sched(amp), loss_scale=65536.0)
+    gpu.set_grads16(np.zeros(n, dtype=np.uint16))
+    gpu.step_f16()
+    st = gpu.read_state()
+    assert st.grad_norm == 0.0 and st.found_inf == 0 and st.skipped == 0 and st.adam_t == 1
+    assert st.clip_coef == 1.0
+
+
+def test_scaler_checks_of_the_reference(G, O):
+    """The expectations of scaler_checks (cuda/tests/test_fast.cu:272-326): an inf gradient skips
+    the step and halves S; the next step runs; growth_interval 2 doubles S back; S = 2^30 halves
+    to 2^29; with dynamic_scale 0 the scale stays."""
+    from cuda_transformer_b200 import amp
+    n = 1 << 16
+    rng = np.random.default_rng(3)
+    init = (rng.standard_normal(n) * 0.02).astype(np.float32)
+    cfg = sched(amp, growth_interval=2000)
+    gpu = G.GpuStep(init, [(0, n, 1)], cfg, loss_scale=65536.0)
+    before = gpu.host()
+    bits = (rng.standard_normal(n) * 1e-3 * 65536.0).astype(np.float16).view(np.uint16)
+    bad = bits.copy()
+    bad[12345 % n] = 0x7C00                                   # +inf
+    gpu.set_grads16(bad)
+    gpu.step_f16()
+    st = gpu.read_state()
+    assert st.found_inf == 1 and st.skipped == 1 and st.adam_t == 0 and st.step == 1
+    assert st.loss_scale == 32768.0 and st.good_steps == 0
+    after = gpu.host()
+    assert all(np.array_equal(a, b) for a, b in zip(before, after))
+    assert not after[1].any()                                 # m did not move
+    gpu.set_grads16((rng.standard_normal(n) * 1e-3 * 32768.0).astype(np.float16).view(np.uint16))
+    gpu.step_f16()
+    st = gpu.read_state()
+    assert st.found_inf == 0 and st.adam_t == 1 and st.step == 2 and st.skipped == 1
+    assert not np.array_equal(gpu.host()[0], before[0])
+    gpu.cfg.growth_interval = 2
+    gpu.step_f16()
+    st = gpu.read_state()
+    assert st.loss_scale == 65536.0 and st.good_steps == 0
+    big = G.GpuStep(init, [(0, n, 1)], cfg, loss_scale=float(2 ** 30))
+    big.set_grads16(bad)
+    big.step_f16()
+    st = big.read_state()
+    assert st.found_inf == 1 and st.skipped == 1 and st.loss_scale == float(2 ** 29)
+    fixed = G.GpuStep(init, [(0, n, 1)], sched(amp, dynamic_scale=0), loss_scale=65536.0)
+    fixed.set_grads16(bad)
+    fixed.step_f16()
+    assert fixed.read_state().loss_scale == 65536.0 and fixed.read_state().skipped == 1
+    # negative infinity and NaN are found too, wherever they sit
+    for pattern, where in ((0xFC00, 0), (0x7E00, n - 1), (0xFFFF, n // 2 + 3)):
+        g = G.GpuStep(init, [(0, n, 1)], cfg, loss_scale=65536.0)
+        b = bits.copy()
+        b[where] = pattern
+        g.set_grads16(b)
+        g.step_f16()
+        assert g.read_state().found_inf == 1, hex(pattern)
+    # the largest finite fp16 is not an overflow
+    g = G.GpuStep(init, [(0, n, 1)], cfg, loss_scale=65536.0)
+    b = bits.copy()
+    b[5] = 0x7BFF
+    b[6] = 0xFBFF
+    g.set_grads16(b)
+    g.step_f16()
+    assert g.read_state().found_inf == 0
+
+
+def test_graph_replay_equals_eager(G):
+    """graph_checks (cuda/tests/test_fast.cu:330-371): capturing runs nothing; 4 replays give the
+    bits of 4 eager steps."""
+    from cuda_transformer_b200 import amp
+    n = 1 << 18
+    rng = np.random.default_rng(11)
+    init = (rng.standard_normal(n) * 0.02).astype(np.float32)
+    bits = (rng.standard_normal(n) * 1e-3 * 65536.0).astype(np.float16).view(np.uint16)
+    table = [(0, n // 2, 1), (n // 2, n // 2, 0)]
+    eager = G.GpuStep(init, table, sched(amp), loss_scale=65536.0)
+    graphed = G.GpuStep(init, table, sched(amp), loss_scale=65536.0)
+    eager.set_grads16(bits)
+    graphed.set_grads16(bits)
+    for _ in range(4):
+        eager.step_f16()
+    stream = torch.cuda.Stream()
+    graph = amp.CudaGraph()
+    assert not graph.ready()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(stream):
+        graph.capture(stream, lambda: graphed.step_f16())
+    assert graph.ready()
+    stream.synchronize()
+    assert graphed.read_state().step == 0, "capturing must not run the step"
+    for _ in range(4):
+        graph.launch(stream)
+    stream.synchronize()
+    a, b = eager.read_state(), graphed.read_state()
+    assert a.step == 4 and b.step == 4 and b.adam_t == 4
+    assert bytes(a) == bytes(b)
+    assert all(np.array_equal(x, y) for x, y in zip(eager.host(), graphed.host()))
+    assert eager.history.cpu().numpy().tobytes() == graphed.history.cpu().numpy().tobytes()
+
+
+def test_result_does_not_depend_on_launch_shape(G):
+    from cuda_transformer_b200 import _lib, amp
+    lib = _lib.load()
+    n = (1 << 22) + 8 * 37
+    rng = np.random.default_rng(5)
+    init = (rng.standard_normal(n) * 0.02).astype(np.float32)
+    bits = (rng.standard_normal(n) * 1e-3 * 65536.0).astype(np.float16).view(np.uint16)
+    table = [(0, 1000, 0), (1000, n - 1000, 1)]
+    results = []
+    knobs = [dict(pass1_blocks_per_sm=8, pass2_blocks_per_sm=4, pass2_unroll=1, pass2_load_hint=0, pass2_store_hint=0),
+             dict(pass1_blocks_per_sm=1, pass2_blocks_per_sm=1, pass2_unroll=2, pass2_load_hint=1, pass2_store_hint=1),
+             dict(pass1_blocks_per_sm=3, pass2_blocks_per_sm=7, pass2_unroll=2, pass2_load_hint=2, pass2_store_hint=0)]
+    defaults = {}
+    for key in knobs[0]:
+        v = C.c_int()
+        _lib.check(lib.b200amp_tune_get(key.encode(), C.byref(v)))
+        defaults[key] = v.value
+    try:
+        for kn in knobs:
+            for key, val in kn.items():
+                _lib.check(lib.b200amp_tune_set(key.encode(), val))
+            g = G.GpuStep(init, table, sched(amp), loss_scale=65536.0)
+            g.set_grads16(bits)
+            g.step_f16()
+            g.step_f16()
+            results.append((bytes(g.read_state()), g.host()))
+    finally:
+        for key, val in defaults.items():
+            lib.b200amp_tune_set(key.encode(), val)
+    for st, arrays in results[1:]:
+        assert st == results[0][0]
+        assert all(np.array_equal(x, y) for x, y in zip(arrays, results[0][1]))
+
+
+def test_sharded_passes_equal_the_whole_arena(G, O):
+    """Pass 2 run as 8 ranges with their arena offsets gives the bits of one launch over the
+    arena; pass 1 partial sums of the ranges, added in rank order, give the same state."""
+    from cuda_transformer_b200 import amp
+    n = 8 * 128 * 523
+    rng = np.random.default_rng(9)
+    init = (rng.standard_normal(n) * 0.02).astype(np.float32)
+    bits = (rng.standard_normal(n) * 1e-3 * 65536.0).astype(np.float16).view(np.uint16)
+    edges = sorted(set([0] + [int(x) * 4 for x in rng.integers(1, n // 4, size=40)]))
+    table = [(a, b - a, i % 2) for i, (a, b) in enumerate(zip(edges, edges[1:] + [n]))]
+    whole = G.GpuStep(init, table, sched(amp), loss_scale=65536.0)
+    whole.set_grads16(bits)
+    whole.step_f16()
+    parts = G.GpuStep(init, table, sched(amp), loss_scale=65536.0)
+    parts.set_grads16(bits)
+    world = 8
+    per = n // world
+    lib_ws = [torch.zeros_like(parts.workspace) for _ in range(world)]
+    sums = torch.zeros(2 * world, dtype=torch.float64, device="cuda")
+    for r in range(world):
+        amp.pass1_f16(parts.grads16[r * per:(r + 1) * per], per, parts.state, lib_ws[r])
+        sums[2 * r:2 * r + 2] = lib_ws[r][:16].view(torch.float64)
+    amp.finalize_sums(parts.state, sums, world, parts.cfg, parts.history, parts.history_len)
+    for r in range(world):
+        sl = slice(r * per, (r + 1) * per)
+        amp.pass2_f16(parts.master[sl], parts.m[sl], parts.v[sl], parts.grads16[sl], parts.weights16[sl], per,
+                      r * per, parts.tensors, parts.ntensors, parts.state, parts.cfg.beta1, parts.cfg.beta2,
+                      parts.eps)
+    a, b = whole.read_state(), parts.read_state()
+    G.assert_states_equal(b, a, tol=1e-6)
+    if a.clip_coef == b.clip_coef:
+        assert all(np.array_equal(x, y) for x, y in zip(whole.host(), parts.host()))
+    else:
+        for x, y in zip(whole.host()[:3], parts.host()[:3]):
+            assert H.rel_err(x, y) <= H.STATE_TOL
+    # an inf in one range only must skip every range
+    bad = bits.copy()
+    bad[5 * per + 17] = 0x7C00
+    parts.set_grads16(bad)
+    for r in range(world):
+        amp.pass1_f16(parts.grads16[r * per:(r + 1) * per], per, parts.state, lib_ws[r])
+        sums[2 * r:2 * r + 2] = lib_ws[r][:16].view(torch.float64)
+    assert [float(sums[2 * r + 1]) for r in range(world)] == [0, 0, 0, 0, 0, 1, 0, 0]
+    amp.finalize_sums(parts.state, sums, world, parts.cfg, parts.history, parts.history_len)
+    assert parts.read_state().found_inf == 1 and parts.read_state().skipped == 1
+
+
+@pytest.mark.parametrize("kind", ["cosine", "wsd"])
+def test_lr_on_gpu_matches_host_schedule(G, O, kind):
+    """GPU lr == host lr_at to 1e-12 (cuda/tests/test_checkpoint.cu:355-437)."""
+    from cuda_transformer_b200 import amp
+    decay_steps = 40 if kind == "wsd" else 0
+    kw = dict(lr=6e-4, min_lr=6e-5, warmup_steps=20, max_steps=200, decay_steps=decay_steps)
+    for step in (0, 1, 19, 20, 21, 100, 159, 160, 161, 199, 200, 5000):
+        assert abs(amp.lr_on_gpu(step, sched(amp, **kw)) - O.lr_at(step, sched(O, **kw))) <= 1e-12
+
+
+def test_bad_arguments_are_errors_not_crashes(G):
+    from cuda_transformer_b200 import _lib, amp
+    g = G.GpuStep(np.zeros(64, dtype=np.float32), [(0, 64, 1)], sched(amp))
+    with pytest.raises(amp.B200AmpError) as e:
+        amp.pass1_finalize_f16(g.grads16, 60, g.state, g.workspace, g.cfg)          # n % 8 != 0
+    assert e.value.status == _lib.ERR_ARG and "multiple of 8" in str(e.value)
+    with pytest.raises(amp.B200AmpError):
+        amp.pass1_finalize_f16(g.grads16.data_ptr() + 2, 56, g.state, g.workspace, g.cfg)   # misaligned
+    with pytest.raises(amp.B200AmpError):
+        amp.pass2_f16(g.master, g.m, g.v, g.grads16, g.weights16, 64, 0, g.tensors, 1025, g.state, 0.9, 0.95, 1e-8)
+    with pytest.raises(amp.B200AmpError):
+        amp.pass2_f16(g.master.data_ptr() + 16, g.m, g.v, g.grads16, g.weights16, 56, 0, g.tensors, 1, g.state,
+                      0.9, 0.95, 1e-8)
+    with pytest.raises(amp.B200AmpError):
+        amp.finalize_step(g.state, g.partial, g.cfg, g.history, 0)                  # history without a length
+    with pytest.raises(amp.B200AmpError):
+        amp.unscale_and_norm(g.master, 0, g.state, g.partial)
+    # the context is still usable
+    g.step_f16()
+    assert g.read_state().step == 1
+
+
+# ---------------------------------------------------------------- the reference's own CUDA kernels
+
+def _ref():
+    from oracle import ref_cuda
+    if not ref_cuda.available():
+        pytest.skip("oracle/_ref/libref_amp.so was not built (no reference checkout at build time)")
+    return ref_cuda, ref_cuda.load()
+
+
+def test_compat_path_is_bit_identical_to_the_reference_kernels(G):
+    """Same fp32 gradients through the reference's kernels (built from its sources for sm_100a)
+    and through the compat entry points: partial[512], the 60 state bytes, the unscaled gradients,
+    params, m, v and the fp16 copy must carry the same bits, step after step, skip included."""
+    from cuda_transformer_b200 import amp
+    from cuda_transformer_b200.layout import CONFIGS, param_layout
+    ref_cuda, ref = _ref()
+    slots = param_layout(CONFIGS["readme"])
+    n = slots[-1].offset + slots[-1].count
+    table = H.table_of(slots)
+    gen = torch.Generator().manual_seed(0)
+    init = (torch.randn(n, generator=gen) * 0.02).numpy()
+    cfg = sched(amp, growth_interval=3)
+    mine = G.GpuStep(init, table, cfg, loss_scale=65536.0)
+    theirs = G.GpuStep(init, table, cfg, loss_scale=65536.0)
+    s = torch.cuda.current_stream().cuda_stream
+    for k in range(6):
+        g = torch.randn(n, generator=gen) * 1e-3 * mine.read_state().loss_scale
+        if k == 2:
+            g[777] = float("inf")
+        g_np = g.numpy()
+        g_mine = mine.step_f32(g_np)
+        g_theirs = G.to_dev(g_np)
+        ref.refamp_begin_step(theirs.state.data_ptr(), s)
+        ref_cuda.optimizer_step(ref, g_theirs.data_ptr(), n, theirs.state.data_ptr(), theirs.partial.data_ptr(),
+                                C.addressof(cfg), theirs.history.data_ptr(), theirs.history_len,
+                                theirs.master.data_ptr(), theirs.weights16.data_ptr(), theirs.m.data_ptr(),
+                                theirs.v.data_ptr(), theirs.tensors.data_ptr(), theirs.ntensors, cfg.beta1,
+                                cfg.beta2, theirs.eps, s)
+        torch.cuda.synchronize()
+        assert torch.equal(mine.partial, theirs.partial) or k == 2, k      # NaN partials never compare equal
+        assert bytes(mine.read_state())[:32] == bytes(theirs.read_state())[:32], k
+        G.assert_states_equal(mine.read_state(), theirs.read_state(), tol=0.0 if k != 2 else 1e-6)
+        if k != 2:
+            assert torch.equal(g_mine, g_theirs), k
+        for a, b in zip(mine.host(), theirs.host()):
+            assert np.array_equal(a, b), k
+    assert mine.read_state().skipped == 1
+
+
+def test_native_path_matches_the_reference_kernels(G):
+    """fp16 gradient arena through the native kernels against the reference's kernels fed
+    float(fp16 gradient): control flow bit-exact, state arrays within 1e-6, fp16 weights 1 ulp."""
+    from cuda_transformer_b200 import amp
+    from cuda_transformer_b200.layout import CONFIGS, param_layout
+    ref_cuda, ref = _ref()
+    slots = param_layout(CONFIGS["readme"])
+    n = slots[-1].offset + slots[-1].count
+    table = H.table_of(slots)
+    gen = torch.Generator().manual_seed(0)
+    init = (torch.randn(n, generator=gen) * 0.02).numpy()
+    cfg = sched(amp, growth_interval=4)
+    mine = G.GpuStep(init, table, cfg, loss_scale=65536.0)
+    theirs = G.GpuStep(init, table, cfg, loss_scale=65536.0)
+    s = torch.cuda.current_stream().cuda_stream
+    identical = 0
+    for k in range(10):
+        g16 = (torch.randn(n, generator=gen) * 1e-3 * mine.read_state().loss_scale).half()
+        if k == 5:
+            g16[123456] = float("nan")
+        mine.grads16.copy_(g16)
+        mine.step_f16()
+        g32 = g16.float().cuda()
+        ref.refamp_begin_step(theirs.state.data_ptr(), s)
+        ref_cuda.optimizer_step(ref, g32.data_ptr(), n, theirs.state.data_ptr(), theirs.partial.data_ptr(),
+                                C.addressof(cfg), theirs.history.data_ptr(), theirs.history_len,
+                                theirs.master.data_ptr(), theirs.weights16.data_ptr(), theirs.m.data_ptr(),
+                                theirs.v.data_ptr(), theirs.tensors.data_ptr(), theirs.ntensors, cfg.beta1,
+                                cfg.beta2, theirs.eps, s)
+        torch.cuda.synchronize()
+        a, b = mine.read_state(), theirs.read_state()
+        G.assert_states_equal(a, b, tol=1e-6)
+        identical += int(a.clip_coef == b.clip_coef)
+    hm, ht = mine.host(), theirs.host()
+    for x, y in zip(hm[:3], ht[:3]):
+        assert H.rel_err(y, x) <= H.STATE_TOL
+    assert H.half_ulp_distance(ht[3], hm[3]) <= 1
+    assert mine.read_state().skipped == 1 and mine.read_state().adam_t == 9
