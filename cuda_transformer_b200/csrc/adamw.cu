@@ -23,24 +23,19 @@ namespace b200amp
 
 constexpr int P2_THREADS = 256;
 
-struct StepScalars
-{
-    float coef, step_size, bc2_sqrt, decay, inv_scale;
-};
-
-// One element. The operation order is the reference's (adamw_multi.cu:20-29): decay the
+// One element, the arithmetic of the reference (cuda/kernels/adamw_multi.cu:20-29): decay the
 // parameter, m += (1-b1)(g-m), v = v*b2 + ((1-b2)*g)*g, denom = sqrt(v)/bc2_sqrt + eps,
-// p = decayed - step_size * (m/denom). The fused multiply-adds are written out so the
-// rounding does not depend on what a compiler chooses to contract; sqrt and both
-// divisions are IEEE round-to-nearest (no fast-math, as in the reference's Makefile:44-46).
+// p = decayed - step_size*(m/denom). Written as plain expressions and built with nvcc's
+// defaults (fused multiply-add contraction on, IEEE sqrt and division: no fast-math, as the
+// reference's Makefile:44-46), so the compiler rounds them the way it rounds the reference's.
 __device__ __forceinline__ void adamw_element(float &p, float &m, float &v, float g, float w1, float w2, float b2,
                                               float eps, float decay, float step_size, float bc2_sqrt)
 {
     const float decayed = p * decay;
-    m = __fmaf_rn(w1, g - m, m);
-    v = __fmaf_rn(v, b2, (w2 * g) * g);
-    const float denom = __fdiv_rn(__fsqrt_rn(v), bc2_sqrt) + eps;
-    p = __fmaf_rn(-step_size, __fdiv_rn(m, denom), decayed);
+    m = m + w1 * (g - m);
+    v = v * b2 + w2 * g * g;
+    const float denom = sqrtf(v) / bc2_sqrt + eps;
+    p = decayed - step_size * (m / denom);
 }
 
 // Tensor table in shared memory + the cursor over it.

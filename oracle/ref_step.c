@@ -12,11 +12,16 @@
  *
  * Each function names the reference lines it restates. `contract` selects how the
  * three multiply-add expressions of the per-element update are rounded:
- *   0  every operation rounded on its own (what torch's CPU AdamW does, and what the
- *      reference's kernels would do if built with -fmad=false);
- *   1  fused where nvcc contracts by default (the reference's Makefile:44-46 keeps
- *      the default): m + w1*(g-m), v*b2 + (w2*g)*g, p*decay - step*(m/denom).
- * The two differ by at most one rounding per operation.
+ *   0      every operation rounded on its own (what torch's CPU AdamW does, and what
+ *          the reference's kernels would do if built with -fmad=false);
+ *   bit 0  fused multiply-adds, as nvcc contracts by default (the reference's
+ *          Makefile:44-46 keeps the default). m + w1*(g-m) has one possible fusion;
+ *          v*b2 + (w2*g)*g and p*decay - step*(m/denom) are each a sum of two products,
+ *          and a compiler may fuse either product:
+ *   bit 1  v: fuse (w2*g)*g instead of v*b2;
+ *   bit 2  p: fuse p*decay instead of step*(m/denom).
+ * Which pair nvcc picks is found on the GPU by the test that compares against the
+ * reference's compiled kernels; all variants differ by at most one rounding per operation.
  */
 #include <math.h>
 #include <stdint.h>
@@ -318,17 +323,31 @@ static inline void adamw_one(float *p, float *m, float *v, float g, float b1, fl
                              float step_size, float bc2_sqrt, int contract)
 {
     float w1 = 1.0f - b1, w2 = 1.0f - b2;
-    float param = *p * decay;
     float mi, vi, denom, out;
-    if (contract)
+    if (contract & 1)
     {
         mi = fmaf(w1, g - *m, *m);
-        vi = fmaf(*v, b2, (w2 * g) * g);
+        if (contract & 2)
+        {
+            vi = fmaf(w2 * g, g, *v * b2);              /* the product v*b2 rounded, the other fused */
+        }
+        else
+        {
+            vi = fmaf(*v, b2, (w2 * g) * g);            /* the product (w2*g)*g rounded, v*b2 fused */
+        }
         denom = sqrtf(vi) / bc2_sqrt + eps;
-        out = fmaf(-step_size, mi / denom, param);
+        if (contract & 4)
+        {
+            out = fmaf(*p, decay, -(step_size * (mi / denom)));     /* p*decay fused, the update rounded */
+        }
+        else
+        {
+            out = fmaf(-step_size, mi / denom, *p * decay);         /* p*decay rounded, the update fused */
+        }
     }
     else
     {
+        float param = *p * decay;
         mi = *m + w1 * (g - *m);
         vi = *v * b2 + (w2 * g) * g;
         denom = sqrtf(vi) / bc2_sqrt + eps;

@@ -471,6 +471,41 @@ def test_bad_arguments_are_errors_not_crashes(G):
     assert g.read_state().step == 1
 
 
+def test_one_oracle_rounding_variant_gives_the_kernel_bits(G, O):
+    """With the clip inactive (coef exactly 1) the step is purely elementwise, so the oracle
+    variant that fuses the same multiply-adds as the compiled kernel must reproduce master, m,
+    v and the fp16 copy bit for bit. Exactly which variant that is gets printed."""
+    from cuda_transformer_b200 import amp
+    n = 1 << 20
+    rng = np.random.default_rng(21)
+    init = (rng.standard_normal(n) * 0.02).astype(np.float32)
+    table = [(0, n // 2, 1), (n // 2, n // 2, 0)]
+    kw = dict(grad_clip=1e30)
+    gpu = G.GpuStep(init, table, sched(amp, **kw), loss_scale=65536.0)
+    variants = {c: O.OracleStep(init, table, sched(O, **kw), loss_scale=65536.0, contract=c) for c in (0, 1, 3, 5, 7)}
+    for _ in range(4):
+        bits = (rng.standard_normal(n) * 1e-3 * 65536.0).astype(np.float16).view(np.uint16)
+        gpu.set_grads16(bits)
+        gpu.step_f16()
+        for o in variants.values():
+            o.step_f16(bits)
+    st = gpu.read_state()
+    hm = gpu.host()
+    matches = []
+    for c, o in variants.items():
+        assert st.clip_coef == 1.0 and o.state.clip_coef == 1.0
+        same_scalars = (st.step_size == o.state.step_size and st.bc2_sqrt == o.state.bc2_sqrt
+                        and st.decay == o.state.decay)
+        same = all(np.array_equal(a, b) for a, b in zip(hm, (o.master, o.m, o.v, o.weights16)))
+        if same and same_scalars:
+            matches.append(c)
+        assert H.rel_err(o.master, hm[0]) <= H.STATE_TOL and H.rel_err(o.m, hm[1]) <= H.STATE_TOL
+        assert H.rel_err(o.v, hm[2]) <= H.STATE_TOL
+    print("oracle contract variants that reproduce the kernel's bits:", matches)
+    assert matches, "no rounding variant of the oracle reproduces the kernel bit for bit"
+    assert 0 not in matches, "the kernel was expected to use fused multiply-adds"
+
+
 # ---------------------------------------------------------------- the reference's own CUDA kernels
 
 def _ref():
