@@ -1,0 +1,29 @@
+"""Runs the C++ host-layer test program (tests/cpp/test_amp_host.cpp) on the GPU."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(HERE, "cpp"))
+
+
+def test_cpp_host_program_builds():
+    """CPU-side: the reference-signature shim and the C++ owner class compile and link against
+    the library (nvcc cross-compiles without a GPU)."""
+    import build as cpp_build
+    from cuda_transformer_b200 import build as lib_build
+    lib_build.build()
+    assert os.path.exists(cpp_build.build())
+
+
+@pytest.mark.gpu
+def test_cpp_host_program_checks_pass():
+    import build as cpp_build
+    exe = cpp_build.build()
+    proc = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    sys.stdout.write(proc.stdout)
+    sys.stderr.write(proc.stderr)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-2000:]
+    assert "all checks passed" in proc.stdout and "FAILED" not in proc.stdout
