@@ -80,6 +80,7 @@ PROTOTYPES = {
     "b200amp_graph_destroy": (_I, [_P]),
     "b200amp_tune_set": (_I, [C.c_char_p, _I]),
     "b200amp_tune_get": (_I, [C.c_char_p, C.POINTER(_I)]),
+    "b200amp_device_error": (_I, [C.POINTER(_I)]),
     "b200amp_launch_count": (_LL, []),
 }
 

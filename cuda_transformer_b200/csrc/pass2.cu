@@ -1,0 +1,577 @@
+// pass2.cu: pass 2 of the step on an fp16 gradient arena: unscale, clip, AdamW on the fp32
+// master / m / v with decoupled weight decay and bias correction, and the fp16 weight
+// cast, in one launch over the flat arena (or over one shard of it).
+//
+// Per element this is cuda/kernels/adamw_multi.cu:20-29,75-89 of the reference. The work
+// is laid out for HBM3e: 28 bytes move per element and nothing else matters. Two kernels
+// do the same arithmetic (same bits):
+//
+//   pass2_f16_kernel   registers only. A persistent grid strides over 8-element groups;
+//                      every access is one 256-bit (fp32 arrays) or 128-bit (fp16 arrays)
+//                      request, so a warp moves 1 KB / 512 B of contiguous memory per
+//                      instruction.
+//   pass2_bulk_kernel  shared-memory staging. One CTA per SM runs a ring of stages; one
+//                      thread moves whole tiles (2048 elements: 4 KB of gradients, 8 KB each
+//                      of master, m, v) with bulk asynchronous copies (cp.async.bulk, no
+//                      multicast) completing on an mbarrier; all threads update the tile in
+//                      place in shared memory; the tile leaves with bulk stores (the fp16
+//                      weights overwrite the gradient slot, which has the same size). Many
+//                      KB in flight per SM without many threads, and every request to DRAM
+//                      is a long contiguous run.
+//
+// The decay flag comes from a cursor into the tensor table that advances as positions
+// grow, instead of a binary search per vector (the search runs once per thread).
+
+#include "adamw_math.cuh"
+
+namespace b200amp
+{
+
+// ---------------------------------------------------------------- registers-only kernel
+
+// BLOCKED false: group i of trip t belongs to CTA (i / THREADS) mod grid (the whole grid sweeps
+// the arena together); true: each CTA owns one contiguous range of the arena.
+template <int THREADS, int UNROLL, int ST, bool BLOCKED>
+__global__ void __launch_bounds__(THREADS)
+    pass2_f16_kernel(float *__restrict__ master, float *__restrict__ m, float *__restrict__ v,
+                     const uint4 *__restrict__ g16, uint4 *__restrict__ w16, long long n8, long long arena_offset,
+                     const b200amp_tensor_info *__restrict__ tensors, int ntensors,
+                     const b200amp_step_state *__restrict__ st, float b1, float b2, float eps)
+{
+    __shared__ TensorTable tab;
+    table_load(tab, tensors, ntensors);
+    if (st->found_inf)
+    {
+        return;                                 // skipped step: nothing moves
+    }
+    const float coef = st->clip_coef;
+    const float step_size = st->step_size;
+    const float bc2_sqrt = st->bc2_sqrt;
+    const float wd_decay = st->decay;
+    const float inv = st->inv_scale;
+    const float w1 = 1.0f - b1;
+    const float w2 = 1.0f - b2;
+
+    long long i, end, stride;
+    if (BLOCKED)
+    {
+        long long per = (n8 + gridDim.x - 1) / gridDim.x;
+        per = (per + THREADS - 1) / THREADS * THREADS;
+        i = static_cast<long long>(blockIdx.x) * per + threadIdx.x;
+        end = static_cast<long long>(blockIdx.x + 1) * per;
+        if (end > n8)
+        {
+            end = n8;
+        }
+        stride = THREADS;
+    }
+    else
+    {
+        stride = static_cast<long long>(gridDim.x) * THREADS;
+        i = static_cast<long long>(blockIdx.x) * THREADS + threadIdx.x;
+        end = n8;
+    }
+    if (i >= end)
+    {
+        return;
+    }
+    Cursor cur = cursor_seek(tab, ntensors, arena_offset + i * 8);
+
+    for (; i < end; i += UNROLL * stride)
+    {
+        uint4 gw[UNROLL];
+        Float8 pp[UNROLL], mm[UNROLL], vv[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++)
+        {
+            const long long j = i + u * stride;
+            if (u == 0 || j < end)
+            {
+                gw[u] = load_h8<0>(g16 + j);
+                pp[u] = load8<0>(master + j * 8);
+                mm[u] = load8<0>(m + j * 8);
+                vv[u] = load8<0>(v + j * 8);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++)
+        {
+            const long long j = i + u * stride;
+            if (u == 0 || j < end)
+            {
+                float d_lo, d_hi;
+                group_decay(cur, tab, ntensors, arena_offset + j * 8, wd_decay, d_lo, d_hi);
+                const uint32_t words[4] = {gw[u].x, gw[u].y, gw[u].z, gw[u].w};
+#pragma unroll
+                for (int k = 0; k < 4; k++)
+                {
+                    const float2 f = half2_bits_to_float2(words[k]);
+                    const float d = k < 2 ? d_lo : d_hi;
+                    // (g16 * inv) is the unscaled fp32 gradient of the reference, then * clip
+                    adamw_element(pp[u].v[2 * k], mm[u].v[2 * k], vv[u].v[2 * k], (f.x * inv) * coef, w1, w2, b2,
+                                  eps, d, step_size, bc2_sqrt);
+                    adamw_element(pp[u].v[2 * k + 1], mm[u].v[2 * k + 1], vv[u].v[2 * k + 1], (f.y * inv) * coef,
+                                  w1, w2, b2, eps, d, step_size, bc2_sqrt);
+                }
+                store8<ST>(master + j * 8, pp[u]);
+                store8<ST>(m + j * 8, mm[u]);
+                store8<ST>(v + j * 8, vv[u]);
+                if (w16 != nullptr)
+                {
+                    uint4 out;
+                    out.x = float2_to_half2_bits(pp[u].v[0], pp[u].v[1]);
+                    out.y = float2_to_half2_bits(pp[u].v[2], pp[u].v[3]);
+                    out.z = float2_to_half2_bits(pp[u].v[4], pp[u].v[5]);
+                    out.w = float2_to_half2_bits(pp[u].v[6], pp[u].v[7]);
+                    store_h8<ST>(w16 + j, out);
+                }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------- shared-memory staged kernel
+
+constexpr int BULK_TILE = 2048;                 // elements per tile
+constexpr int BULK_THREADS = 512;               // one quad (4 elements) per thread per tile
+constexpr int BULK_MAX_STAGES = 7;
+constexpr unsigned BULK_WAIT_LIMIT = 1u << 22;  // polls of one barrier before the kernel gives up
+
+struct __align__(128) BulkStage
+{
+    float p[BULK_TILE];
+    float m[BULK_TILE];
+    float v[BULK_TILE];
+    __half g[BULK_TILE];                        // gradients in, fp16 weights out
+};
+static_assert(sizeof(BulkStage) == 14 * BULK_TILE, "a stage holds 14 bytes per element (updated in place)");
+
+// Set when a barrier wait ran out (a copy that never completed). Read by b200amp_device_error().
+__device__ int g_bulk_timeout = 0;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p)
+{
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, unsigned count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" : : "r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, unsigned bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" : : "r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, unsigned parity)
+{
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(smem_u32(bar)), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+
+// Bounded wait: true when the phase completed, false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity)
+{
+    for (unsigned tries = 0; tries < BULK_WAIT_LIMIT; tries++)
+    {
+        if (mbar_try_wait(bar, parity))
+        {
+            return true;
+        }
+        if (tries > 64)
+        {
+            __nanosleep(64);
+        }
+    }
+    return false;
+}
+
+// global -> shared, completes `bytes` on the barrier. No multicast: the destination is this CTA's
+// own shared memory (a CTA launched without a cluster is a cluster of one).
+__device__ __forceinline__ void bulk_load(void *dst_smem, const void *src_gmem, unsigned bytes, uint64_t *bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :
+                 : "r"(smem_u32(dst_smem)), "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// shared -> global, tracked by the thread's bulk async-group
+__device__ __forceinline__ void bulk_store(void *dst_gmem, const void *src_smem, unsigned bytes)
+{
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                 :
+                 : "l"(dst_gmem), "r"(smem_u32(src_smem)), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void bulk_commit()
+{
+    asm volatile("cp.async.bulk.commit_group;" : : : "memory");
+}
+
+template <int PENDING>
+__device__ __forceinline__ void bulk_wait_read()        // at most PENDING store groups still reading shared memory
+{
+    asm volatile("cp.async.bulk.wait_group.read %0;" : : "n"(PENDING) : "memory");
+}
+
+__device__ __forceinline__ void bulk_wait_all()
+{
+    asm volatile("cp.async.bulk.wait_group 0;" : : : "memory");
+}
+
+__device__ __forceinline__ void fence_async_proxy()     // generic-proxy writes to shared memory -> async proxy
+{
+    asm volatile("fence.proxy.async.shared::cta;" : : : "memory");
+}
+
+// Tile t of the range holds elements [t * BULK_TILE, min(n, (t + 1) * BULK_TILE)). CTA b owns tiles
+// b, b + grid, b + 2 grid, ... Stage of the k-th owned tile: k mod stages.
+__global__ void __launch_bounds__(BULK_THREADS, 1)
+    pass2_bulk_kernel(float *__restrict__ master, float *__restrict__ m, float *__restrict__ v,
+                      const __half *__restrict__ g16, __half *__restrict__ w16, long long n, long long arena_offset,
+                      const b200amp_tensor_info *__restrict__ tensors, int ntensors,
+                      const b200amp_step_state *__restrict__ st, float b1, float b2, float eps, int stages)
+{
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    BulkStage *stage = reinterpret_cast<BulkStage *>(smem_raw);
+    __shared__ TensorTable tab;
+    __shared__ uint64_t full[BULK_MAX_STAGES];
+    __shared__ int gave_up;
+
+    table_load(tab, tensors, ntensors);
+    if (st->found_inf)
+    {
+        return;                                 // skipped step: nothing moves
+    }
+    const float coef = st->clip_coef;
+    const float step_size = st->step_size;
+    const float bc2_sqrt = st->bc2_sqrt;
+    const float wd_decay = st->decay;
+    const float inv = st->inv_scale;
+    const float w1 = 1.0f - b1;
+    const float w2 = 1.0f - b2;
+
+    const long long ntiles = (n + BULK_TILE - 1) / BULK_TILE;
+    const long long first_tile = blockIdx.x;
+    if (first_tile >= ntiles)
+    {
+        return;
+    }
+    const long long my_tiles = (ntiles - first_tile + gridDim.x - 1) / gridDim.x;
+    const int lookahead = stages - 2;           // loads in flight; one stage computes, one drains its stores
+
+    if (threadIdx.x == 0)
+    {
+        for (int s = 0; s < stages; s++)
+        {
+            mbar_init(&full[s], 1);
+        }
+        gave_up = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" : : : "memory");
+    }
+    __syncthreads();
+
+    auto tile_elems = [&](long long k) -> unsigned
+    {
+        const long long begin = (first_tile + k * gridDim.x) * BULK_TILE;
+        const long long left = n - begin;
+        return static_cast<unsigned>(left < BULK_TILE ? left : BULK_TILE);
+    };
+    auto issue_load = [&](long long k)
+    {
+        const long long begin = (first_tile + k * gridDim.x) * BULK_TILE;
+        const unsigned cnt = tile_elems(k);
+        BulkStage &sg = stage[k % stages];
+        uint64_t *bar = &full[k % stages];
+        mbar_expect_tx(bar, cnt * 14u);
+        bulk_load(sg.g, g16 + begin, cnt * 2u, bar);
+        bulk_load(sg.p, master + begin, cnt * 4u, bar);
+        bulk_load(sg.m, m + begin, cnt * 4u, bar);
+        bulk_load(sg.v, v + begin, cnt * 4u, bar);
+    };
+
+    if (threadIdx.x == 0)
+    {
+        for (long long k = 0; k < lookahead && k < my_tiles; k++)
+        {
+            issue_load(k);
+        }
+    }
+
+    Cursor cur = cursor_seek(tab, ntensors, arena_offset + first_tile * BULK_TILE);
+    long long done = 0;                         // tiles whose barrier this thread has passed
+    for (long long k = 0; k < my_tiles; k++)
+    {
+        if (threadIdx.x == 0 && k + lookahead < my_tiles)
+        {
+            // the stage about to be refilled held tile k + lookahead - stages = k - 2: its stores
+            // were committed two trips ago; all but the latest store group must be done reading
+            bulk_wait_read<1>();
+            issue_load(k + lookahead);
+        }
+        BulkStage &sg = stage[k % stages];
+        const unsigned parity = static_cast<unsigned>((k / stages) & 1);
+        if (!mbar_wait(&full[k % stages], parity))
+        {
+            gave_up = 1;                        // every thread that timed out stores the same value
+        }
+        __syncthreads();
+        if (gave_up)
+        {
+            break;
+        }
+        done = k + 1;
+
+        const long long tile_begin = (first_tile + k * gridDim.x) * BULK_TILE;
+        const unsigned cnt = tile_elems(k);
+        const long long at0 = arena_offset + tile_begin;
+        cursor_advance(cur, tab, ntensors, at0);
+        const bool uniform = at0 + cnt <= cur.next;
+        const float d_tile = tab.decay[cur.k] ? wd_decay : 1.0f;
+
+        const unsigned q = threadIdx.x;         // quad of this thread: BULK_TILE / 4 == BULK_THREADS
+        if (q * 4 < cnt)
+        {
+            float d = d_tile;
+            if (!uniform)
+            {
+                Cursor c2 = cur;
+                cursor_advance(c2, tab, ntensors, at0 + q * 4);
+                d = tab.decay[c2.k] ? wd_decay : 1.0f;
+            }
+            float4 p4 = reinterpret_cast<float4 *>(sg.p)[q];
+            float4 m4 = reinterpret_cast<float4 *>(sg.m)[q];
+            float4 v4 = reinterpret_cast<float4 *>(sg.v)[q];
+            const uint2 gq = reinterpret_cast<const uint2 *>(sg.g)[q];
+            const float2 g01 = half2_bits_to_float2(gq.x);
+            const float2 g23 = half2_bits_to_float2(gq.y);
+            adamw_element(p4.x, m4.x, v4.x, (g01.x * inv) * coef, w1, w2, b2, eps, d, step_size, bc2_sqrt);
+            adamw_element(p4.y, m4.y, v4.y, (g01.y * inv) * coef, w1, w2, b2, eps, d, step_size, bc2_sqrt);
+            adamw_element(p4.z, m4.z, v4.z, (g23.x * inv) * coef, w1, w2, b2, eps, d, step_size, bc2_sqrt);
+            adamw_element(p4.w, m4.w, v4.w, (g23.y * inv) * coef, w1, w2, b2, eps, d, step_size, bc2_sqrt);
+            reinterpret_cast<float4 *>(sg.p)[q] = p4;
+            reinterpret_cast<float4 *>(sg.m)[q] = m4;
+            reinterpret_cast<float4 *>(sg.v)[q] = v4;
+            uint2 wq;
+            wq.x = float2_to_half2_bits(p4.x, p4.y);
+            wq.y = float2_to_half2_bits(p4.z, p4.w);
+            reinterpret_cast<uint2 *>(sg.g)[q] = wq;
+        }
+        fence_async_proxy();
+        __syncthreads();
+        if (threadIdx.x == 0)
+        {
+            bulk_store(master + tile_begin, sg.p, cnt * 4u);
+            bulk_store(m + tile_begin, sg.m, cnt * 4u);
+            bulk_store(v + tile_begin, sg.v, cnt * 4u);
+            if (w16 != nullptr)
+            {
+                bulk_store(w16 + tile_begin, sg.g, cnt * 2u);
+            }
+            bulk_commit();
+        }
+    }
+
+    if (threadIdx.x == 0)
+    {
+        bulk_wait_all();                        // stores of this thread: complete before the CTA leaves
+        if (gave_up)
+        {
+            g_bulk_timeout = 1;
+            // loads already issued still target this CTA's shared memory: give each one more bounded
+            // wait before the memory is handed back
+            long long issued = done + lookahead < my_tiles ? done + lookahead : my_tiles;
+            for (long long k = done; k < issued; k++)
+            {
+                mbar_wait(&full[k % stages], static_cast<unsigned>((k / stages) & 1));
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------- launch
+
+template <int THREADS, int UNROLL>
+static void launch_registers(int st_hint, bool blocked, int grid, cudaStream_t s, float *master, float *m, float *v,
+                             const uint4 *g16, uint4 *w16, long long n8, long long arena_offset,
+                             const b200amp_tensor_info *tensors, int ntensors, const b200amp_step_state *st, float b1,
+                             float b2, float eps)
+{
+#define B200AMP_P2(ST, BL)                                                                                       \
+    pass2_f16_kernel<THREADS, UNROLL, ST, BL><<<grid, THREADS, 0, s>>>(master, m, v, g16, w16, n8, arena_offset, \
+                                                                       tensors, ntensors, st, b1, b2, eps)
+    if (st_hint == 1 && blocked)
+    {
+        B200AMP_P2(1, true);
+    }
+    else if (st_hint == 1)
+    {
+        B200AMP_P2(1, false);
+    }
+    else if (blocked)
+    {
+        B200AMP_P2(0, true);
+    }
+    else
+    {
+        B200AMP_P2(0, false);
+    }
+#undef B200AMP_P2
+}
+
+template <int THREADS>
+static void launch_registers_unroll(int unroll, int st_hint, bool blocked, int grid, cudaStream_t s, float *master,
+                                    float *m, float *v, const uint4 *g16, uint4 *w16, long long n8,
+                                    long long arena_offset, const b200amp_tensor_info *tensors, int ntensors,
+                                    const b200amp_step_state *st, float b1, float b2, float eps)
+{
+    // only the shapes that fit the register file without spilling are built:
+    // 256 threads x 1/2/4 groups, 512 x 1/2, 1024 x 1
+    if constexpr (THREADS == 256)
+    {
+        if (unroll >= 4)
+        {
+            launch_registers<THREADS, 4>(st_hint, blocked, grid, s, master, m, v, g16, w16, n8, arena_offset,
+                                         tensors, ntensors, st, b1, b2, eps);
+            return;
+        }
+    }
+    if constexpr (THREADS <= 512)
+    {
+        if (unroll >= 2)
+        {
+            launch_registers<THREADS, 2>(st_hint, blocked, grid, s, master, m, v, g16, w16, n8, arena_offset,
+                                         tensors, ntensors, st, b1, b2, eps);
+            return;
+        }
+    }
+    launch_registers<THREADS, 1>(st_hint, blocked, grid, s, master, m, v, g16, w16, n8, arena_offset, tensors,
+                                 ntensors, st, b1, b2, eps);
+}
+
+static int bulk_smem_bytes(int stages)
+{
+    return stages * static_cast<int>(sizeof(BulkStage));
+}
+
+static int prepare_bulk(int stages)
+{
+    // opt in to more than 48 KB of dynamic shared memory, once per device and stage count
+    constexpr int MAX_DEVICES = 64;
+    static int prepared[MAX_DEVICES] = {};
+    int dev = 0;
+    B200AMP_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEVICES)
+    {
+        set_error("device index %d out of range", dev);
+        return B200AMP_ERR_ARG;
+    }
+    if (prepared[dev] != stages)
+    {
+        B200AMP_CUDA(cudaFuncSetAttribute(pass2_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          bulk_smem_bytes(stages)));
+        prepared[dev] = stages;
+    }
+    return B200AMP_OK;
+}
+
+} // namespace b200amp
+
+using namespace b200amp;
+
+extern "C" B200AMP_API int b200amp_pass2_f16(float *master, float *m, float *v, const void *grads16, void *weights16,
+                                             long long n, long long arena_offset, const b200amp_tensor_info *tensors,
+                                             int ntensors, const b200amp_step_state *st, float beta1, float beta2,
+                                             float eps, b200amp_stream s)
+{
+    B200AMP_REQUIRE(master != nullptr && m != nullptr && v != nullptr && grads16 != nullptr && st != nullptr,
+                    "pass 2: null pointer");
+    B200AMP_REQUIRE(n > 0 && n % 8 == 0, "pass 2: n = %lld must be a positive multiple of 8", n);
+    B200AMP_REQUIRE(arena_offset >= 0 && arena_offset % 4 == 0, "pass 2: arena_offset = %lld must be a multiple of 4",
+                    arena_offset);
+    B200AMP_REQUIRE(aligned(master, 32) && aligned(m, 32) && aligned(v, 32),
+                    "pass 2: master, m and v must be 32-byte aligned");
+    B200AMP_REQUIRE(aligned(grads16, 16) && aligned(weights16, 16),
+                    "pass 2: the fp16 arenas must be 16-byte aligned");
+    B200AMP_REQUIRE(tensors != nullptr, "pass 2: tensor table is null");
+    B200AMP_REQUIRE(ntensors > 0 && ntensors <= B200AMP_MAX_TENSORS, "pass 2: ntensors = %d, must be in 1..%d",
+                    ntensors, B200AMP_MAX_TENSORS);
+    const int sms = sm_count();
+    if (sms <= 0)
+    {
+        return B200AMP_ERR_CUDA;
+    }
+    const Tunables &t = tunables();
+    cudaStream_t stream = as_stream(s);
+
+    if (t.pass2_variant == 1)
+    {
+        const int stages = t.pass2_stages;
+        int rc = prepare_bulk(stages);
+        if (rc != B200AMP_OK)
+        {
+            return rc;
+        }
+        const long long ntiles = (n + BULK_TILE - 1) / BULK_TILE;
+        int grid = sms;
+        if (grid > ntiles)
+        {
+            grid = static_cast<int>(ntiles);
+        }
+        pass2_bulk_kernel<<<grid, BULK_THREADS, bulk_smem_bytes(stages), stream>>>(
+            master, m, v, static_cast<const __half *>(grads16), static_cast<__half *>(weights16), n, arena_offset,
+            tensors, ntensors, st, beta1, beta2, eps, stages);
+        B200AMP_LAUNCHED();
+        return B200AMP_OK;
+    }
+
+    const long long n8 = n / 8;
+    const int threads = t.pass2_threads;
+    long long want = (n8 + threads - 1) / threads;
+    int grid = sms * t.pass2_blocks_per_sm;
+    if (grid > want)
+    {
+        grid = static_cast<int>(want);
+    }
+    const uint4 *g16 = static_cast<const uint4 *>(grads16);
+    uint4 *w16 = static_cast<uint4 *>(weights16);
+    const bool blocked = t.pass2_partition == 1;
+    if (threads == 1024)
+    {
+        launch_registers_unroll<1024>(t.pass2_unroll, t.pass2_store_hint, blocked, grid, stream, master, m, v, g16,
+                                      w16, n8, arena_offset, tensors, ntensors, st, beta1, beta2, eps);
+    }
+    else if (threads == 512)
+    {
+        launch_registers_unroll<512>(t.pass2_unroll, t.pass2_store_hint, blocked, grid, stream, master, m, v, g16,
+                                     w16, n8, arena_offset, tensors, ntensors, st, beta1, beta2, eps);
+    }
+    else
+    {
+        launch_registers_unroll<256>(t.pass2_unroll, t.pass2_store_hint, blocked, grid, stream, master, m, v, g16,
+                                     w16, n8, arena_offset, tensors, ntensors, st, beta1, beta2, eps);
+    }
+    B200AMP_LAUNCHED();
+    return B200AMP_OK;
+}
+
+// 1 if a shared-memory staged launch on the current device gave up waiting for a copy since
+// the library was loaded. Synchronises the device.
+extern "C" B200AMP_API int b200amp_device_error(int *out)
+{
+    B200AMP_REQUIRE(out != nullptr, "device_error: out is null");
+    int flag = 0;
+    B200AMP_CUDA(cudaMemcpyFromSymbol(&flag, g_bulk_timeout, sizeof(int)));
+    *out = flag;
+    return B200AMP_OK;
+}

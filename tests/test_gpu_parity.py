@@ -367,9 +367,15 @@ def test_result_does_not_depend_on_launch_shape(G):
     bits = (rng.standard_normal(n) * 1e-3 * 65536.0).astype(np.float16).view(np.uint16)
     table = [(0, 1000, 0), (1000, n - 1000, 1)]
     results = []
-    knobs = [dict(pass1_blocks_per_sm=8, pass2_blocks_per_sm=4, pass2_unroll=1, pass2_load_hint=0, pass2_store_hint=0),
-             dict(pass1_blocks_per_sm=1, pass2_blocks_per_sm=1, pass2_unroll=2, pass2_load_hint=1, pass2_store_hint=1),
-             dict(pass1_blocks_per_sm=3, pass2_blocks_per_sm=7, pass2_unroll=2, pass2_load_hint=2, pass2_store_hint=0)]
+    base = dict(pass1_blocks_per_sm=8, pass2_blocks_per_sm=4, pass2_unroll=1, pass2_store_hint=0, pass2_threads=256,
+                pass2_partition=0, pass2_variant=0, pass2_stages=6)
+    knobs = [base,
+             dict(base, pass1_blocks_per_sm=1, pass2_blocks_per_sm=1, pass2_unroll=2, pass2_store_hint=1),
+             dict(base, pass1_blocks_per_sm=3, pass2_blocks_per_sm=7, pass2_unroll=4, pass2_partition=1),
+             dict(base, pass2_threads=512, pass2_unroll=2, pass2_blocks_per_sm=1, pass2_partition=1),
+             dict(base, pass2_threads=1024, pass2_blocks_per_sm=1),
+             dict(base, pass2_variant=1, pass2_stages=6),
+             dict(base, pass2_variant=1, pass2_stages=3)]
     defaults = {}
     for key in knobs[0]:
         v = C.c_int()
@@ -390,6 +396,9 @@ def test_result_does_not_depend_on_launch_shape(G):
     for st, arrays in results[1:]:
         assert st == results[0][0]
         assert all(np.array_equal(x, y) for x, y in zip(arrays, results[0][1]))
+    flag = C.c_int(-1)
+    _lib.check(lib.b200amp_device_error(C.byref(flag)))
+    assert flag.value == 0, "a staged launch gave up waiting for a bulk copy"
 
 
 def test_sharded_passes_equal_the_whole_arena(G, O):
