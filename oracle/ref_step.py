@@ -16,10 +16,7 @@ import sys
 
 import numpy as np
 
-_HERE = os.path.dirname(os.path.abspath(__file__))
-if _HERE not in sys.path:
-    sys.path.insert(0, _HERE)
-import build as _oracle_build  # noqa: E402  (oracle/build.py)
+from . import build as _oracle_build    # oracle/build.py
 
 
 class StepState(C.Structure):

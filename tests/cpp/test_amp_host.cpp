@@ -5,7 +5,7 @@
 //     scaler_checks (cuda/tests/test_fast.cu:272-326);
 //   * b200amp_host::AmpOptimizer (fp16 gradient arena) against the shim path on the same values;
 //   * graph_checks (cuda/tests/test_fast.cu:330-371): capture runs nothing, replays equal eager.
-// Needs a GPU. Built by tests/cpp/build.py, run by tests/test_gpu_host_cpp.py.
+// Needs a GPU. Built by tests/cpp/build_host_test.py, run by tests/test_gpu_host_cpp.py.
 #include <cmath>
 #include <cstdint>
 #include <cstdio>

@@ -12,16 +12,17 @@ sys.path.insert(0, os.path.join(HERE, "cpp"))
 def test_cpp_host_program_builds():
     """CPU-side: the reference-signature shim and the C++ owner class compile and link against
     the library (nvcc cross-compiles without a GPU)."""
-    import build as cpp_build
+    import build_host_test
     from cuda_transformer_b200 import build as lib_build
     lib_build.build()
-    assert os.path.exists(cpp_build.build())
+    exe = build_host_test.build()
+    assert os.path.exists(exe) and exe.endswith("test_amp_host")
 
 
 @pytest.mark.gpu
 def test_cpp_host_program_checks_pass():
-    import build as cpp_build
-    exe = cpp_build.build()
+    import build_host_test
+    exe = build_host_test.build()
     proc = subprocess.run([exe], capture_output=True, text=True, timeout=600)
     sys.stdout.write(proc.stdout)
     sys.stderr.write(proc.stderr)
