@@ -11,17 +11,21 @@ namespace b200amp
 
 // One element, the arithmetic of the reference (cuda/kernels/adamw_multi.cu:20-29): decay the
 // parameter, m += (1-b1)(g-m), v = v*b2 + ((1-b2)*g)*g, denom = sqrt(v)/bc2_sqrt + eps,
-// p = decayed - step_size*(m/denom). Written as plain expressions and built with nvcc's
-// defaults (fused multiply-add contraction on, IEEE sqrt and division: no fast-math, as the
-// reference's Makefile:44-46), so the compiler rounds them the way it rounds the reference's.
+// p = decayed - step_size*(m/denom). The reference builds with nvcc's defaults (fused
+// multiply-add contraction on; IEEE sqrt and division, no fast-math: Makefile:44-46). The
+// fusions nvcc 12.9 picks for those expressions are written out here with intrinsics, so every
+// kernel that inlines this function rounds identically whatever code surrounds it: the single
+// fusion of m + w1*(g-m); in v, the product (w2*g)*g fused and v*b2 rounded; in p, the product
+// step_size*(m/denom) fused and p*decay rounded. The GPU tests hold this to the bits of the
+// reference's own kernels compiled from its sources.
 __device__ __forceinline__ void adamw_element(float &p, float &m, float &v, float g, float w1, float w2, float b2,
                                               float eps, float decay, float step_size, float bc2_sqrt)
 {
-    const float decayed = p * decay;
-    m = m + w1 * (g - m);
-    v = v * b2 + w2 * g * g;
-    const float denom = sqrtf(v) / bc2_sqrt + eps;
-    p = decayed - step_size * (m / denom);
+    const float decayed = __fmul_rn(p, decay);
+    m = __fmaf_rn(w1, __fsub_rn(g, m), m);
+    v = __fmaf_rn(__fmul_rn(w2, g), g, __fmul_rn(v, b2));
+    const float denom = __fadd_rn(__fdiv_rn(__fsqrt_rn(v), bc2_sqrt), eps);
+    p = __fmaf_rn(-step_size, __fdiv_rn(m, denom), decayed);
 }
 
 // Tensor table in shared memory + the cursor over it.

@@ -393,9 +393,15 @@ def test_result_does_not_depend_on_launch_shape(G):
     finally:
         for key, val in defaults.items():
             lib.b200amp_tune_set(key.encode(), val)
-    for st, arrays in results[1:]:
-        assert st == results[0][0]
-        assert all(np.array_equal(x, y) for x, y in zip(arrays, results[0][1]))
+    different = []
+    for idx, (st, arrays) in enumerate(results[1:], start=1):
+        if st != results[0][0]:
+            different.append((idx, "state"))
+        for name, x, y in zip(("master", "m", "v", "weights16"), arrays, results[0][1]):
+            if not np.array_equal(x, y):
+                bad = np.flatnonzero(x != y)
+                different.append((idx, name, int(bad.size), int(bad[0]), int(bad[-1])))
+    assert not different, f"launch shapes (index into knobs) that changed the result: {different}"
     flag = C.c_int(-1)
     _lib.check(lib.b200amp_device_error(C.byref(flag)))
     assert flag.value == 0, "a staged launch gave up waiting for a bulk copy"
