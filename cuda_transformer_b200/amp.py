@@ -34,7 +34,7 @@ __all__ = [
     "StepState", "ScheduleConfig", "TensorInfo", "B200AmpError",
     "initial_state", "begin_step", "unscale_and_norm", "finalize_step", "adamw_multi", "lr_on_gpu",
     "cast_to_x", "CudaGraph", "AmpOptimizer", "Zero1Step", "ShardedAmpOptimizer", "make_schedule",
-    "pass1_f16", "pass1_finalize_f16", "finalize_sums", "pass2_f16", "step_f16",
+    "pass1_f16", "pass1_f16_static", "pass1_finalize_f16", "finalize_sums", "pass2_f16", "step_f16",
 ]
 
 
@@ -118,6 +118,12 @@ def cast_to_x(out_f16, inp_f32, n: int, stream=None) -> None:
 
 def pass1_f16(grads16, n: int, st, workspace, stream=None) -> None:
     check(_lib.load().b200amp_pass1_f16(_ptr(grads16), n, _ptr(st), _ptr(workspace), _stream(stream)))
+
+
+def pass1_f16_static(grads16, n: int, st, sums_out, stream=None) -> None:
+    """Pass 1 on the library's own scratch: for callers that cannot allocate device memory.
+    sums_out: device memory for two doubles {sum of squares, flag}. See include/b200amp.h."""
+    check(_lib.load().b200amp_pass1_f16_static(_ptr(grads16), n, _ptr(st), _ptr(sums_out), _stream(stream)))
 
 
 def pass1_finalize_f16(grads16, n: int, st, workspace, cfg: ScheduleConfig, history=None, history_len: int = 0,

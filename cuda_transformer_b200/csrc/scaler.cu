@@ -568,3 +568,82 @@ extern "C" B200AMP_API int b200amp_finalize_sums(b200amp_step_state *st, const d
     B200AMP_LAUNCHED();
     return B200AMP_OK;
 }
+
+// ---------------------------------------------------------------- pass 1 without a caller-supplied workspace
+//
+// For callers that cannot hand the library any device memory beyond the arrays the step itself
+// reads and writes, and cannot allocate more: a trainer that gave all of the device's memory to
+// its own arenas when it started (the reference's FastGPT allocates everything in its
+// constructor and nothing afterwards), a plugin running inside another framework's memory
+// pool, or a step loop where cudaMalloc's implicit device-wide synchronisation is not
+// acceptable. The scratch that pass 1 needs (one fp64 partial per virtual block, the ticket, the
+// flag word) lives in the library image instead: every GPU that loads the library holds these
+// 37,920 bytes until the process exits.
+
+#include <mutex>
+
+namespace b200amp
+{
+
+constexpr long long STATIC_PASS1_MAX_ELEMENTS = 1LL << 32;     // 4,294,967,296 fp16 gradients (8 GiB)
+
+static __device__ __align__(256) unsigned char g_pass1_scratch[sizeof(Workspace)];
+
+// The device address of g_pass1_scratch on the current device. In host code the array's name
+// is only a handle for the runtime, not a pointer a kernel could use, so the address is asked
+// for once per device (with that device current) and kept.
+static int pass1_scratch_address(Workspace **out)
+{
+    constexpr int MAX_DEVICES = 64;
+    static Workspace *known[MAX_DEVICES] = {};
+    static std::mutex guard;
+    int dev = -1;
+    B200AMP_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEVICES)
+    {
+        set_error("pass1_f16_static: device index %d out of range", dev);
+        return B200AMP_ERR_ARG;
+    }
+    std::lock_guard<std::mutex> hold(guard);
+    if (known[dev] == nullptr)
+    {
+        void *address = nullptr;
+        B200AMP_CUDA(cudaGetSymbolAddress(&address, g_pass1_scratch));
+        known[dev] = static_cast<Workspace *>(address);
+    }
+    *out = known[dev];
+    return B200AMP_OK;
+}
+
+} // namespace b200amp
+
+extern "C" B200AMP_API int b200amp_pass1_f16_static(const void *grads16, long long n, const b200amp_step_state *st,
+                                                    double *sums_out, b200amp_stream s)
+{
+    B200AMP_REQUIRE(sums_out != nullptr, "pass1_f16_static: sums_out is null");
+    B200AMP_REQUIRE(aligned(sums_out, 8), "pass1_f16_static: sums_out must be 8-byte aligned");
+    if (n > STATIC_PASS1_MAX_ELEMENTS)
+    {
+        set_error("pass1_f16_static: n = %lld is beyond the %lld elements this entry point accepts; "
+                  "use b200amp_pass1_f16 with a workspace of your own",
+                  n, STATIC_PASS1_MAX_ELEMENTS);
+        return B200AMP_ERR_LIMIT;
+    }
+    Workspace *scratch = nullptr;
+    int rc = pass1_scratch_address(&scratch);
+    if (rc != B200AMP_OK)
+    {
+        return rc;
+    }
+    cudaStream_t stream = as_stream(s);
+    // The array keeps whatever the last call left. The kernel resets its ticket and flag itself
+    // when it finishes; clearing them here too makes a call independent of how the last one ended.
+    B200AMP_CUDA(cudaMemsetAsync(&scratch->ticket, 0, sizeof(scratch->ticket) + sizeof(scratch->bad), stream));
+    rc = launch_pass1(grads16, n, const_cast<b200amp_step_state *>(st), scratch, false, nullptr, nullptr, 0, stream);
+    if (rc != B200AMP_OK)
+    {
+        return rc;
+    }
+    B200AMP_CUDA(cudaMemcpyAsync(sums_out, scratch->sums, 2 * sizeof(double), cudaMemcpyDeviceToDevice, stream));
+    return B200AMP_OK;
+}

@@ -171,6 +171,24 @@ B200AMP_API int b200amp_workspace_init(void *workspace, b200amp_stream s);
 B200AMP_API int b200amp_pass1_f16(const void *grads16, long long n, const b200amp_step_state *st, void *workspace,
                       b200amp_stream s);
 
+/* Pass 1 for callers that cannot allocate device memory and have none to spare for a
+ * workspace (everything was handed to their own arenas at start-up, or they run inside
+ * another framework's memory pool, or cudaMalloc's device-wide synchronisation is not
+ * acceptable in their step loop). This entry point has no counterpart in the reference.
+ * Same arithmetic and summation order as b200amp_pass1_f16, so the same bits; the scratch
+ * is a 37,920-byte array inside the library image (each GPU that loads the library holds it
+ * until the process exits). On return of the stream work sums_out[0..1] (DEVICE memory,
+ * caller-owned, 8-byte aligned) hold {sum of squares, flag as 0.0 / 1.0}.
+ *   - Calls cudaMalloc / cudaFree or any allocating routine: never.
+ *   - n at most 4,294,967,296 elements; larger n returns B200AMP_ERR_LIMIT (use
+ *     b200amp_pass1_f16 with your own workspace).
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress). Make that first call outside any stream capture.
+ *   - All calls on a device share the one array: two calls whose GPU work overlaps (different
+ *     streams, no ordering between them) race on it. Serialise them. */
+B200AMP_API int b200amp_pass1_f16_static(const void *grads16, long long n, const b200amp_step_state *st,
+                                         double *sums_out, b200amp_stream s);
+
 /* Finalize from nranks pairs {sum of squares, flag} laid out rank after rank
  * (device memory, e.g. the output of an all-gather of every rank's first 16
  * workspace bytes). Pairs are added in rank order, so every rank computes the
