@@ -164,6 +164,7 @@ def run_gpu(args) -> dict:
     from cuda_transformer_b200 import _lib, amp
     from cuda_transformer_b200.layout import padded
 
+    fused = False
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -189,7 +190,9 @@ def run_gpu(args) -> dict:
         amp.cast_to_x(opt.weights16, opt.master, n)
         step_fn = opt.optimizer_step
     else:
-        opt = amp.ShardedAmpOptimizer(slots, cfg, eps=1e-8, loss_scale=loss_scale, device=dev)
+        fused = args.collectives == "fused"
+        make = amp.FusedZero1Optimizer if fused else amp.ShardedAmpOptimizer
+        opt = make(slots, cfg, eps=1e-8, loss_scale=loss_scale, device=dev)
         # the same master values as the 1-GPU run would hold in this slice would need the whole
         # stream; a per-rank seed gives the same distribution, which is all the timing needs
         fill_normal_(opt.master, 0.02, seed=100 + rank)
@@ -252,6 +255,19 @@ def run_gpu(args) -> dict:
             amp.pass2_f16(opt.master, opt.m, opt.v, opt.grads16, opt.weights16, opt.n, 0, opt.tensors,
                           opt.ntensors, opt.state, opt.beta1, opt.beta2, opt.eps)
             ev[k][2].record()
+    elif fused:
+        for k in range(args.steps):
+            ev[k][0].record()
+            opt._barrier("grads16")
+            opt.fused_pass1()
+            ev[k][1].record()
+            opt._barrier("pairs")
+            opt.finalize_pairs()
+            ev[k][2].record()
+            opt.fused_pass2()
+            ev[k][3].record()
+            opt._barrier("weights16")
+            ev[k][4].record()
     else:
         for k in range(args.steps):
             ev[k][0].record()
@@ -282,6 +298,17 @@ def run_gpu(args) -> dict:
     if world == 1:
         pass1_ms, pass2_ms = avg(0, 1), avg(1, 2)
         n_local = n
+    elif fused:
+        # each fused kernel is timed with the barrier in front of it: a rank that arrives early waits there
+        phases = {"barrier_rs_pass1_ms": max_over_ranks(avg(0, 1)), "barrier_finalize_ms": max_over_ranks(avg(1, 2)),
+                  "pass2_ag_ms": max_over_ranks(avg(2, 3)), "barrier_end_ms": max_over_ranks(avg(3, 4))}
+        pass1_ms, pass2_ms = phases["barrier_rs_pass1_ms"], phases["pass2_ag_ms"]
+        n_local = opt.n_local
+        coll_bytes = (world - 1) / world * 2 * n            # per GPU per direction, each fused kernel
+        phases["rs_pass1_nvlink_gbs"] = coll_bytes / (phases["barrier_rs_pass1_ms"] * 1e-3) / 1e9
+        phases["pass2_ag_nvlink_gbs"] = coll_bytes / (phases["pass2_ag_ms"] * 1e-3) / 1e9
+        phases["nvlink_peak_gbs"] = NVLINK_MEASURED_GBS
+        phases["collectives"] = "fused into the passes: plain peer loads (rs_pass1) and peer stores (pass2_ag)"
     else:
         phases = {"reduce_scatter_ms": max_over_ranks(avg(0, 1)), "pass1_ms": max_over_ranks(avg(1, 2)),
                   "norm_gather_finalize_ms": max_over_ranks(avg(2, 3)), "pass2_ms": max_over_ranks(avg(3, 4)),
@@ -292,6 +319,7 @@ def run_gpu(args) -> dict:
         phases["reduce_scatter_gbs"] = coll_bytes / (phases["reduce_scatter_ms"] * 1e-3) / 1e9
         phases["all_gather_gbs"] = coll_bytes / (phases["all_gather_ms"] * 1e-3) / 1e9
         phases["nvlink_peak_gbs"] = NVLINK_MEASURED_GBS
+        phases["collectives"] = "NCCL reduce_scatter_tensor(AVG) / all_gather_into_tensor around the passes"
     st = opt.read_state()
     if st.skipped != 0:
         raise SystemExit("a timed step was skipped: the timing would count 2 B/param steps")
@@ -357,6 +385,23 @@ def run_gpu(args) -> dict:
     line["roofline"]["traffic"] = PASS2_DRAM_BYTES_PER_PARAM_NCU * n_local
     line["roofline"]["traffic_source"] = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on the "
                                           "gpt2-small arena (profiles/), scaled by the element count")
+    if world > 1 and fused:
+        # A fused compute + collective kernel: its floor is the slower of the HBM time of its slice and
+        # the time its bytes need on NVLink (measured peer bandwidth per direction per GPU).
+        link_bytes = (world - 1) / world * 2 * n
+        t_hbm = BYTES_PASS2 * n_local / (peak * 1e9)
+        t_link = link_bytes / (NVLINK_MEASURED_GBS * 1e9)
+        by_link = t_link > t_hbm
+        achieved = (link_bytes if by_link else BYTES_PASS2 * n_local) / (pass2_ms * 1e-3) / 1e9
+        bound_peak = NVLINK_MEASURED_GBS if by_link else peak
+        line["roofline"].update({
+            "bound": "nvlink" if by_link else "hbm", "kernel": "pass2_ag_f16_kernel", "achieved": achieved,
+            "peak": bound_peak, "frac": achieved / bound_peak,
+            "peak_kind": ("measured peer-copy bandwidth per direction" if by_link
+                          else f"{peak_kind} copy bandwidth"),
+            "floor_ms": {"hbm": t_hbm * 1e3, "nvlink": t_link * 1e3}, "traffic": None,
+            "traffic_source": None, "nvlink_bytes_per_launch": link_bytes})
+        line["kernels_ms"] = {"barrier+rs_pass1": pass1_ms, "pass2_ag": pass2_ms}
     if world > 1:
         dist.destroy_process_group()
     return line if rank == 0 else None
@@ -370,6 +415,9 @@ def main() -> None:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", default="1.3b", choices=["debug", "readme", "gpt2-small", "1.3b"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--collectives", choices=["fused", "nccl"], default="fused",
+                    help="N > 1: fold reduce-scatter / all-gather into the passes (peer loads and stores), "
+                         "or call NCCL around them")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))

@@ -73,6 +73,8 @@ PROTOTYPES = {
     "b200amp_finalize_sums": (_I, [_P, _P, _I, C.POINTER(ScheduleConfig), _P, _I, _P]),
     "b200amp_pass1_finalize_f16": (_I, [_P, _LL, _P, _P, C.POINTER(ScheduleConfig), _P, _I, _P]),
     "b200amp_pass2_f16": (_I, [_P, _P, _P, _P, _P, _LL, _LL, _P, _I, _P, _F, _F, _F, _P]),
+    "b200amp_rs_pass1_f16": (_I, [_P, _I, _I, _P, _LL, _P, _P, _P, _P]),
+    "b200amp_pass2_ag_f16": (_I, [_P, _P, _P, _P, _P, _I, _LL, _LL, _P, _I, _P, _F, _F, _F, _P]),
     "b200amp_step_f16": (_I, [_P, _P, _P, _P, _P, _LL, _P, _I, _P, _P, C.POINTER(ScheduleConfig), _P, _I,
                               _F, _F, _F, _P]),
     "b200amp_graph_begin_capture": (_I, [_P]),

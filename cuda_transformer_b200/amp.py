@@ -34,7 +34,7 @@ __all__ = [
     "StepState", "ScheduleConfig", "TensorInfo", "B200AmpError",
     "initial_state", "begin_step", "unscale_and_norm", "finalize_step", "adamw_multi", "lr_on_gpu",
     "cast_to_x", "CudaGraph", "AmpOptimizer", "Zero1Step", "ShardedAmpOptimizer", "make_schedule",
-    "pass1_f16", "pass1_f16_static", "pass1_finalize_f16", "finalize_sums", "pass2_f16", "step_f16",
+    "pass1_f16", "pass1_f16_static", "pass1_finalize_f16", "rs_pass1_f16", "pass2_ag_f16", "FusedZero1Optimizer", "finalize_sums", "pass2_f16", "step_f16",
 ]
 
 
@@ -143,6 +143,30 @@ def pass2_f16(master, m, v, grads16, weights16, n: int, arena_offset: int, tenso
     check(_lib.load().b200amp_pass2_f16(_ptr(master), _ptr(m), _ptr(v), _ptr(grads16), _ptr(weights16), n,
                                         arena_offset, _ptr(tensors), ntensors, _ptr(st), beta1, beta2, eps,
                                         _stream(stream)))
+
+
+def _pointer_array(pointers: Sequence[int]):
+    return (C.c_void_p * len(pointers))(*[C.c_void_p(int(p)) for p in pointers])
+
+
+def rs_pass1_f16(grads16_by_rank: Sequence[int], my_rank: int, reduced16, n: int, st, workspace,
+                 pair_table_by_rank: Optional[Sequence[int]] = None, stream=None) -> None:
+    """Reduce-scatter + pass 1 in one kernel. grads16_by_rank[r]: device pointer (valid in THIS process)
+    to the start of this rank's slice in rank r's gradient arena."""
+    tables = _pointer_array(pair_table_by_rank) if pair_table_by_rank is not None else None
+    check(_lib.load().b200amp_rs_pass1_f16(_pointer_array(grads16_by_rank), len(grads16_by_rank), my_rank,
+                                           _ptr(reduced16), n, _ptr(st), _ptr(workspace), tables,
+                                           _stream(stream)))
+
+
+def pass2_ag_f16(master, m, v, reduced16, weights16_by_rank: Sequence[int], n: int, arena_offset: int, tensors,
+                 ntensors: int, st, beta1: float, beta2: float, eps: float, stream=None) -> None:
+    """Pass 2 + all-gather in one kernel. weights16_by_rank[r]: device pointer to the start of this
+    rank's slice in rank r's weight arena (own arena included)."""
+    check(_lib.load().b200amp_pass2_ag_f16(_ptr(master), _ptr(m), _ptr(v), _ptr(reduced16),
+                                           _pointer_array(weights16_by_rank), len(weights16_by_rank), n,
+                                           arena_offset, _ptr(tensors), ntensors, _ptr(st), beta1, beta2, eps,
+                                           _stream(stream)))
 
 
 def step_f16(master, m, v, grads16, weights16, n: int, tensors, ntensors: int, st, workspace,
@@ -329,14 +353,19 @@ class Zero1Step:
         self.master = torch.zeros(self.n_local, dtype=torch.float32, device=dev)
         self.m = torch.zeros_like(self.master)
         self.v = torch.zeros_like(self.master)
-        self.weights16 = torch.zeros(self.n, dtype=torch.float16, device=dev)
-        self.grads16 = torch.zeros(self.n, dtype=torch.float16, device=dev)
+        self.weights16 = self._alloc_arena16("weights16")
+        self.grads16 = self._alloc_arena16("grads16")
         self.grad_shard = torch.zeros(self.n_local, dtype=torch.float16, device=dev)
         self.state = torch.zeros(C.sizeof(StepState), dtype=torch.uint8, device=dev)
         self.history = torch.zeros(C.sizeof(StepState) * history_len, dtype=torch.uint8, device=dev)
         self.sums_local = torch.zeros(2, dtype=torch.float64, device=dev)      # {sum of squares, flag}
         self.sums_all = torch.zeros(2 * self.world, dtype=torch.float64, device=dev)
         self.reset(loss_scale)
+
+    def _alloc_arena16(self, name: str) -> torch.Tensor:
+        """A full-length fp16 arena (gradients or weights). Subclasses that map the arenas into
+        the other ranks' address spaces allocate them differently."""
+        return torch.zeros(self.n, dtype=torch.float16, device=self.device)
 
     # -- compute hooks, bound by the subclass
     def _pass1(self) -> None:
@@ -444,3 +473,78 @@ class ShardedAmpOptimizer(Zero1Step):
     def optimizer_step(self) -> None:
         with torch.cuda.device(self.device):
             super().optimizer_step()
+
+
+class FusedZero1Optimizer(ShardedAmpOptimizer):
+    """ZeRO-1 with the collectives folded into the two passes (b200amp_rs_pass1_f16,
+    b200amp_pass2_ag_f16) instead of NCCL calls around them.
+
+    The fp16 gradient arena, the fp16 weight arena and the table of {sum, flag} pairs are
+    allocated as symmetric memory (torch.distributed._symmetric_memory): every rank's buffers
+    are mapped into every process, so a kernel reads a peer's gradients and writes a peer's
+    weights with ordinary loads and stores over NVLink. One step on each rank, all on one stream:
+
+        barrier                      every rank's gradients are in its arena
+        rs_pass1                     pull + average my slice, norm partials, pairs -> every table
+        barrier                      every pair has landed in every table
+        finalize_sums                replicated, rank-ordered: identical state bits everywhere
+        pass2_ag                     AdamW on my slice, fp16 weights -> every arena
+        barrier                      every slice has landed in every weight arena
+
+    The barriers are the symmetric-memory handle's (signal pads, stream-ordered, with a
+    timeout); the kernels themselves never wait on another GPU. The averaged gradient is
+    rounded to fp16 once from an fp32 sum, so it is at least as accurate as an fp16 NCCL
+    reduction; norm and flag are taken on exactly the stored averaged values.
+    """
+
+    BARRIER_TIMEOUT_MS = 10_000
+
+    def __init__(self, slots: List[ParamSlot], cfg: ScheduleConfig, eps: float = 1e-8,
+                 loss_scale: float = 65536.0, history_len: int = 256, device=None, group=None):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        self._symm_mem = symm_mem
+        self._symm_group = group if group is not None else dist.group.WORLD
+        self._handles = {}
+        super().__init__(slots, cfg, eps, loss_scale, history_len, device, group)
+        with torch.cuda.device(self.device):
+            self.pairs = symm_mem.empty(2 * self.world, dtype=torch.float64, device=self.device)
+            self.pairs.zero_()
+            self._handles["pairs"] = symm_mem.rendezvous(self.pairs, self._symm_group)
+            for name in ("grads16", "weights16"):
+                self._handles[name] = symm_mem.rendezvous(getattr(self, name), self._symm_group)
+            shard_bytes = self.begin * 2
+            self._grad_ptrs = [int(p) + shard_bytes for p in self._handles["grads16"].buffer_ptrs]
+            self._weight_ptrs = [int(p) + shard_bytes for p in self._handles["weights16"].buffer_ptrs]
+            self._pair_ptrs = [int(p) for p in self._handles["pairs"].buffer_ptrs]
+            torch.cuda.current_stream().synchronize()
+            self._barrier("pairs")
+
+    def _alloc_arena16(self, name: str) -> torch.Tensor:
+        with torch.cuda.device(self.device):
+            t = self._symm_mem.empty(self.n, dtype=torch.float16, device=self.device)
+            t.zero_()
+            return t
+
+    def _barrier(self, which: str) -> None:
+        self._handles[which].barrier(channel=0, timeout_ms=self.BARRIER_TIMEOUT_MS)
+
+    def fused_pass1(self) -> None:
+        rs_pass1_f16(self._grad_ptrs, self.rank, self.grad_shard, self.n_local, self.state, self.workspace,
+                     self._pair_ptrs)
+
+    def fused_pass2(self) -> None:
+        pass2_ag_f16(self.master, self.m, self.v, self.grad_shard, self._weight_ptrs, self.n_local, self.begin,
+                     self.tensors, self.ntensors, self.state, self.beta1, self.beta2, self.eps)
+
+    def finalize_pairs(self) -> None:
+        finalize_sums(self.state, self.pairs, self.world, self.sched, self.history, self.history_len)
+
+    def optimizer_step(self) -> None:
+        with torch.cuda.device(self.device):
+            self._barrier("grads16")
+            self.fused_pass1()
+            self._barrier("pairs")
+            self.finalize_pairs()
+            self.fused_pass2()
+            self._barrier("weights16")

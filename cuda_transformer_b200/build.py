@@ -21,8 +21,9 @@ INCLUDE_DIR = os.path.join(REPO_DIR, "include")
 LIB_DIR = os.path.join(PKG_DIR, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libb200amp.so")
 
-SOURCES = ["api.cu", "scaler.cu", "adamw.cu", "pass2.cu"]
+SOURCES = ["api.cu", "scaler.cu", "adamw.cu", "pass2.cu", "zero1.cu"]
 HEADERS = [os.path.join(CSRC_DIR, "internal.cuh"), os.path.join(CSRC_DIR, "adamw_math.cuh"),
+           os.path.join(CSRC_DIR, "pass1_common.cuh"),
            os.path.join(INCLUDE_DIR, "b200amp.h")]
 
 NVCC_FLAGS = [

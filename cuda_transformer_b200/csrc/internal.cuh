@@ -31,6 +31,8 @@ struct Tunables
     int pass2_partition;        // 0: the grid sweeps the arena together, 1: one contiguous range per CTA
     int pass2_variant;          // 0: registers-only kernel, 1: shared-memory staged kernel (bulk async copies)
     int pass2_stages;           // ring depth of the staged kernel: 3..7 (28 KB each)
+    int rs_blocks_per_sm;       // resident CTAs per SM of the fused reduce-scatter + pass 1
+    int ag_blocks_per_sm;       // resident CTAs per SM of the fused pass 2 + all-gather
 };
 Tunables &tunables();
 

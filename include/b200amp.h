@@ -214,6 +214,33 @@ B200AMP_API int b200amp_pass2_f16(float *master, float *m, float *v, const void 
                       long long arena_offset, const b200amp_tensor_info *tensors, int ntensors,
                       const b200amp_step_state *st, float beta1, float beta2, float eps, b200amp_stream s);
 
+/* ---------------------------------------------------------------- ZeRO-1 with the collectives folded in
+ * For R = 1, 2, 4 or 8 GPUs of one NVLink box, one process per GPU, with every rank's fp16
+ * gradient arena, fp16 weight arena and pair table mapped into every process (CUDA IPC /
+ * symmetric memory: the pointers below are ordinary device pointers of the CALLING process).
+ * The reference has no multi-GPU code; per element these are pass 1 and pass 2 above. Neither
+ * kernel waits on another GPU: the caller orders the ranks with stream-ordered barriers
+ * (gradients of all ranks ready -> rs_pass1; all rs_pass1 done -> finalize_sums; all pass2_ag
+ * done -> weights may be read). All remote accesses are plain 128-bit loads and stores. */
+
+/* Reduce-scatter + pass 1. grads16_by_rank[r] (HOST array of nranks device pointers) is the
+ * start of THIS rank's slice in rank r's gradient arena. The slice is averaged over the ranks
+ * (fp32 sum in rank order, * 1/nranks, one rounding to fp16) into reduced16 (local, n
+ * elements); the squared norm and inf/NaN flag of those stored values go to the workspace
+ * (first 16 bytes, as b200amp_pass1_f16) and, if pair_table_by_rank is not null, into entry
+ * my_rank of every rank's pair table (pair_table_by_rank[r]: nranks pairs of doubles). */
+B200AMP_API int b200amp_rs_pass1_f16(const void *const *grads16_by_rank, int nranks, int my_rank, void *reduced16,
+                                     long long n, const b200amp_step_state *st, void *workspace,
+                                     double *const *pair_table_by_rank, b200amp_stream s);
+
+/* Pass 2 + all-gather. As b200amp_pass2_f16 on the rank's slice, with the fp16 weights stored
+ * to weights16_by_rank[r] for every r (HOST array of nranks device pointers: the start of this
+ * rank's slice in rank r's weight arena, the rank's own arena included). */
+B200AMP_API int b200amp_pass2_ag_f16(float *master, float *m, float *v, const void *reduced16,
+                                     void *const *weights16_by_rank, int nranks, long long n, long long arena_offset,
+                                     const b200amp_tensor_info *tensors, int ntensors, const b200amp_step_state *st,
+                                     float beta1, float beta2, float eps, b200amp_stream s);
+
 /* The whole step for an arena held by one GPU: b200amp_pass1_finalize_f16 then
  * b200amp_pass2_f16 (two launches). */
 B200AMP_API int b200amp_step_f16(float *master, float *m, float *v, const void *grads16, void *weights16, long long n,
