@@ -1,0 +1,124 @@
+"""Builds the REFERENCE's own test programs for sm_100a, twice: as they are ("stock"), and with
+the reference's optimizer objects replaced by the link shim over libb200amp.so ("b200amp").
+
+    python oracle/build_ref_tests.py [/path/to/cuda-transformer]
+
+Everything is compiled from the reference checkout where it lies (its Makefile's FAST_SRC list,
+-DFP16, -arch changed from sm_75 to sm_100a; Makefile:44-48,93-117); objects and binaries go to
+oracle/_ref/ (git-ignored). Nothing of the reference is copied into this repository. Also writes
+the answer-key dump the programs read (oracle/_ref/data/debug.bin) by running the reference's
+own reference/dump.py on the random-token fallback its tests use. Without the checkout this is a
+no-op.
+
+    stock:    common dump gpt weights data kernels/*.cu gpt_fast graph checkpoint  + test_X.cu
+    b200amp:  the same minus kernels/scaler.cu, kernels/adamw_multi.cu, graph.cu
+              plus oracle/link_shim.cu and -lb200amp
+"""
+from __future__ import annotations
+
+import concurrent.futures
+import glob
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REPO = os.path.dirname(HERE)
+OUT = os.path.join(HERE, "_ref")
+OBJ = os.path.join(OUT, "obj")
+BIN = os.path.join(OUT, "bin")
+DUMP = os.path.join(OUT, "data", "debug.bin")
+DEFAULT_REF = "/root/reference"
+REPLACED = ("kernels/scaler.cu", "kernels/adamw_multi.cu", "graph.cu")
+PROGRAMS = ("test_fast", "test_checkpoint")
+
+
+def _nvcc() -> str:
+    return shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+
+
+def _compile(src: str, obj: str, includes) -> None:
+    if os.path.exists(obj) and os.path.getmtime(obj) >= os.path.getmtime(src):
+        return
+    os.makedirs(os.path.dirname(obj), exist_ok=True)
+    cmd = [_nvcc(), "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-DFP16"]
+    for inc in includes:
+        cmd += ["-I", inc]
+    cmd += ["-c", src, "-o", obj]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("compile failed: " + " ".join(cmd) + "\n" + proc.stderr[-4000:])
+
+
+def binaries() -> dict:
+    return {f"{prog}_{kind}": os.path.join(BIN, f"{prog}_{kind}") for prog in PROGRAMS for kind in ("stock", "b200amp")}
+
+
+def available() -> bool:
+    return all(os.path.exists(p) for p in binaries().values()) and os.path.exists(DUMP)
+
+
+def write_dump(ref_root: str) -> str:
+    """The tiny answer key (L2 H4 C64, B4 T64, perturbed 1-D parameters) through the reference's
+    own dump module, on 100,000 seeded random token ids (reference/test_reference.py:40-45)."""
+    if os.path.exists(DUMP):
+        return DUMP
+    os.makedirs(os.path.dirname(DUMP), exist_ok=True)
+    code = (
+        "import sys, numpy as np\n"
+        f"sys.path.insert(0, {ref_root!r})\n"
+        "from reference import dump\n"
+        "from reference.config import DUMP_BATCH, TrainConfig, tiny_model_config\n"
+        "rng = np.random.default_rng(0)\n"
+        "tokens = rng.integers(0, 4098, size=100_000).astype(np.uint16)\n"
+        "header, records = dump.build_records(tiny_model_config(4098), TrainConfig(), tokens, DUMP_BATCH, 'cpu', "
+        "perturb=True)\n"
+        f"dump.write_dump({DUMP!r}, header, records)\n")
+    env = dict(os.environ, PYTHONDONTWRITEBYTECODE="1")
+    proc = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env)
+    if proc.returncode != 0:
+        raise RuntimeError("writing the reference dump failed:\n" + proc.stderr[-4000:])
+    return DUMP
+
+
+def build(ref_root: str = DEFAULT_REF, jobs: int = 8):
+    """Dict name -> path of the four binaries, or None without the reference checkout."""
+    cuda = os.path.join(ref_root, "cuda")
+    if not os.path.exists(os.path.join(cuda, "gpt_fast.cu")):
+        return binaries() if available() else None
+    from cuda_transformer_b200 import build as lib_build
+    lib_build.build()
+    rel = ["common.cu", "dump.cu", "gpt.cu", "weights.cu", "data.cu", "gpt_fast.cu", "graph.cu", "checkpoint.cu"]
+    rel += sorted("kernels/" + os.path.basename(p) for p in glob.glob(os.path.join(cuda, "kernels", "*.cu")))
+    rel += [f"tests/{prog}.cu" for prog in PROGRAMS]
+    includes = [cuda, os.path.join(ref_root, "tokenizer")]
+    jobs_list = [(os.path.join(cuda, r), os.path.join(OBJ, r[:-3] + ".o"), includes) for r in rel]
+    shim_obj = os.path.join(OBJ, "link_shim.o")
+    jobs_list.append((os.path.join(HERE, "link_shim.cu"), shim_obj, includes + [os.path.join(REPO, "include")]))
+    with concurrent.futures.ThreadPoolExecutor(max_workers=jobs) as pool:
+        for f in [pool.submit(_compile, *job) for job in jobs_list]:
+            f.result()
+    os.makedirs(BIN, exist_ok=True)
+    common = [r for r in rel if not r.startswith("tests/")]
+    lib_dir = os.path.join(REPO, "cuda_transformer_b200", "lib")
+    out = binaries()
+    for prog in PROGRAMS:
+        test_obj = os.path.join(OBJ, f"tests/{prog}.o")
+        stock = [os.path.join(OBJ, r[:-3] + ".o") for r in common]
+        ours = [os.path.join(OBJ, r[:-3] + ".o") for r in common if r not in REPLACED] + [shim_obj]
+        for kind, objs, extra in (("stock", stock, []),
+                                  ("b200amp", ours, ["-L", lib_dir, "-lb200amp", "-Xlinker", "-rpath", "-Xlinker",
+                                                     "$ORIGIN/../../../cuda_transformer_b200/lib"])):
+            cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-o", out[f"{prog}_{kind}"], test_obj] + \
+                objs + extra
+            proc = subprocess.run(cmd, capture_output=True, text=True)
+            if proc.returncode != 0:
+                raise RuntimeError("link failed: " + " ".join(cmd) + "\n" + proc.stderr[-4000:])
+    write_dump(ref_root)
+    return out
+
+
+if __name__ == "__main__":
+    sys.path.insert(0, REPO)
+    print(build(sys.argv[1] if len(sys.argv) > 1 else DEFAULT_REF))
