@@ -116,6 +116,25 @@ def _rank_main(rank, world, port, out_dir):
             both = [torch.zeros_like(mine) for _ in range(world)]
             dist.all_gather(both, mine)
             assert all(torch.equal(both[0], b) for b in both)
+        # ---- sharded state -> one GPTC checkpoint -> back into fresh shards (cuda/checkpoint.cu:288-315)
+        from cuda_transformer_b200 import checkpoint as ck
+        full = ck.checkpoint_of(z, ck.ModelShape(4098, 4160, 64, 2, 4, 64, 1e-5), ck.RunInfo(B=4))
+        assert full.params.size == z.n_params and bytes(full.state) == bytes(z.read_state())
+        assert np.array_equal(full.m[z.begin:min(z.end, z.n_params)], z.m.numpy()[: max(0, min(z.end, z.n_params) - z.begin)])
+        assert H.rel_err(single.master[: z.n_params], full.params) <= H.STATE_TOL
+        path = os.path.join(out_dir, f"zero1_rank{rank}.ckpt")
+        ck.write_checkpoint(path, full)
+        z2 = OracleZero1(slots, cfg, eps=1e-8, loss_scale=1.0, history_len=16, device="cpu", group=None)
+        ck.restore(z2, ck.read_checkpoint(path))
+        g = (torch.randn(z.n, generator=gen) * 1e-3 * z.read_state().loss_scale).half()
+        g[z.n_params:] = 0
+        for o in (z, z2):
+            o.grads16.copy_(g)
+            o.optimizer_step()
+        assert bytes(z.read_state()) == bytes(z2.read_state())
+        assert torch.equal(z.master, z2.master) and torch.equal(z.m, z2.m) and torch.equal(z.v, z2.v)
+        assert torch.equal(z.weights16, z2.weights16)
+        z.write_state(full.state)       # the counters the assertions below look at
         st = z.read_state()
         assert st.skipped == 1 and st.adam_t == STEPS - 1 and st.loss_scale == 32768.0 and st.good_steps == 2
         open(os.path.join(out_dir, f"ok{rank}"), "w").write("ok")
