@@ -32,7 +32,7 @@ struct Tunables
     int pass2_variant;          // 0: registers-only kernel, 1: shared-memory staged kernel (bulk async copies)
     int pass2_stages;           // ring depth of the staged kernel: 3..7 (28 KB each)
     int rs_blocks_per_sm;       // resident CTAs per SM of the fused reduce-scatter + pass 1
-    int ag_blocks_per_sm;       // resident CTAs per SM of the fused pass 2 + all-gather
+    int ag_blocks_per_sm;       // resident CTAs per SM of the fused pass 2 + all-gather, 0 = by rank count
 };
 Tunables &tunables();
 

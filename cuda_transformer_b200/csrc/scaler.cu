@@ -214,6 +214,9 @@ __global__ void lr_probe_kernel(double *out, int step, b200amp_schedule cfg)
 // ---------------------------------------------------------------- native pass 1
 
 // (partition, workspace layout and the 8-value accumulation: pass1_common.cuh)
+#ifndef B200AMP_P1_LOAD_HINT
+#define B200AMP_P1_LOAD_HINT 1
+#endif
 
 // FINALIZE: the last block also runs finalize_state (one GPU holds the whole arena).
 // Otherwise it only publishes {sum, flag} in the workspace (a shard of a larger arena).
@@ -251,7 +254,7 @@ __global__ void __launch_bounds__(P1_THREADS)
 #pragma unroll
             for (int u = 0; u < P1_UNROLL; u++)
             {
-                w[u] = load_h8<1>(g8 + i + u * P1_THREADS);
+                w[u] = load_h8<B200AMP_P1_LOAD_HINT>(g8 + i + u * P1_THREADS);
             }
 #pragma unroll
             for (int u = 0; u < P1_UNROLL; u++)
@@ -265,7 +268,7 @@ __global__ void __launch_bounds__(P1_THREADS)
         {
             if (i + u * P1_THREADS < end)
             {
-                uint4 w = load_h8<1>(g8 + i + u * P1_THREADS);
+                uint4 w = load_h8<B200AMP_P1_LOAD_HINT>(g8 + i + u * P1_THREADS);
                 accumulate_h8(w, inv, acc[u], bad);
             }
         }

@@ -67,7 +67,16 @@ __device__ __forceinline__ uint4 average_h8(const uint4 (&w)[R], float inv_ranks
     return out;
 }
 
-constexpr int RS_UNROLL = 2;        // vectors per thread per trip: R * RS_UNROLL 16-byte loads in flight
+#ifndef B200AMP_RS_UNROLL
+#define B200AMP_RS_UNROLL 2
+#endif
+#ifndef B200AMP_RS_LOAD_HINT
+#define B200AMP_RS_LOAD_HINT 0          // plain ld.global: measured 5 % faster over NVLink than .nc.L1::no_allocate
+#endif
+#ifndef B200AMP_AG_STORE_HINT
+#define B200AMP_AG_STORE_HINT 0
+#endif
+constexpr int RS_UNROLL = B200AMP_RS_UNROLL;    // vectors per thread per trip: R * RS_UNROLL 16-byte loads in flight
 
 // src.p[r]: the start of THIS rank's slice inside rank r's gradient arena. reduced: local.
 // pair_tables.p[r]: rank r's table of R pairs {sum, flag}; this rank fills entry my_rank of each.
@@ -115,7 +124,7 @@ __global__ void __launch_bounds__(P1_THREADS)
 #pragma unroll
                         for (int r = 0; r < R; r++)
                         {
-                            w[u][r] = load_h8<1>(static_cast<const uint4 *>(src.p[r]) + i);
+                            w[u][r] = load_h8<B200AMP_RS_LOAD_HINT>(static_cast<const uint4 *>(src.p[r]) + i);
                         }
                     }
                 }
@@ -220,7 +229,7 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
         for (int r = 0; r < R; r++)
         {
-            store_h8<0>(static_cast<uint4 *>(dst.p[r]) + i, out);
+            store_h8<B200AMP_AG_STORE_HINT>(static_cast<uint4 *>(dst.p[r]) + i, out);
         }
     }
 }
@@ -324,7 +333,14 @@ extern "C" B200AMP_API int b200amp_pass2_ag_f16(float *master, float *m, float *
     }
     const long long n8 = n / 8;
     long long want = (n8 + 255) / 256;
-    int grid = sms * tunables().ag_blocks_per_sm;
+    // 0 = choose by what binds the kernel: two ranks leave it HBM-bound (2 CTAs/SM, as pass 2 alone);
+    // from four ranks on it is NVLink-bound and more CTAs keep more peer stores in flight
+    int per_sm = tunables().ag_blocks_per_sm;
+    if (per_sm <= 0)
+    {
+        per_sm = nranks <= 2 ? 2 : 16;
+    }
+    int grid = sms * per_sm;
     if (grid > want)
     {
         grid = static_cast<int>(want);
