@@ -49,6 +49,7 @@ struct Cursor
 {
     int k;              // the last tensor whose first element is <= the position (0 if none is)
     long long next;     // first element of tensor k + 1, LLONG_MAX past the end
+    float factor;       // what a parameter of tensor k is multiplied by: the step's decay, or 1
 };
 
 __device__ __forceinline__ long long table_next(const TensorTable &tab, int ntensors, int k)
@@ -56,7 +57,7 @@ __device__ __forceinline__ long long table_next(const TensorTable &tab, int nten
     return k + 1 < ntensors ? tab.first[k + 1] : LLONG_MAX;
 }
 
-__device__ __forceinline__ Cursor cursor_seek(const TensorTable &tab, int ntensors, long long at)
+__device__ __forceinline__ Cursor cursor_seek(const TensorTable &tab, int ntensors, long long at, float wd_decay)
 {
     int lo = 0, hi = ntensors - 1;
     while (lo < hi)
@@ -74,31 +75,46 @@ __device__ __forceinline__ Cursor cursor_seek(const TensorTable &tab, int ntenso
     Cursor c;
     c.k = lo;
     c.next = table_next(tab, ntensors, lo);
+    c.factor = tab.decay[lo] ? wd_decay : 1.0f;
     return c;
 }
 
-__device__ __forceinline__ void cursor_advance(Cursor &c, const TensorTable &tab, int ntensors, long long at)
+// Positions only grow. Nothing to do (one compare, no shared-memory access) while the
+// position stays inside tensor k, which is the case for all but a few hundred trips.
+__device__ __forceinline__ void cursor_advance(Cursor &c, const TensorTable &tab, int ntensors, long long at,
+                                               float wd_decay)
 {
-    while (at >= c.next)
+    if (at >= c.next)
     {
-        c.k += 1;
-        c.next = table_next(tab, ntensors, c.k);
+        do
+        {
+            c.k += 1;
+            c.next = table_next(tab, ntensors, c.k);
+        } while (at >= c.next);
+        c.factor = tab.decay[c.k] ? wd_decay : 1.0f;
     }
 }
 
 // Decay factors of the two quads of the 8-element group that starts at `at`. Tensor
 // offsets are multiples of 4, so a quad never straddles two tensors but a group can.
+// The usual case, the whole group inside the cursor's tensor, costs one compare.
 __device__ __forceinline__ void group_decay(Cursor &c, const TensorTable &tab, int ntensors, long long at,
                                             float wd_decay, float &lo, float &hi)
 {
-    cursor_advance(c, tab, ntensors, at);
-    lo = tab.decay[c.k] ? wd_decay : 1.0f;
-    hi = lo;
+    if (at + 8 <= c.next)
+    {
+        lo = c.factor;
+        hi = c.factor;
+        return;
+    }
+    cursor_advance(c, tab, ntensors, at, wd_decay);
+    lo = c.factor;
+    hi = c.factor;
     if (at + 4 >= c.next)
     {
         Cursor c2 = c;
-        cursor_advance(c2, tab, ntensors, at + 4);
-        hi = tab.decay[c2.k] ? wd_decay : 1.0f;
+        cursor_advance(c2, tab, ntensors, at + 4, wd_decay);
+        hi = c2.factor;
     }
 }
 

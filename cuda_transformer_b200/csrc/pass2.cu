@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(THREADS)
     {
         return;
     }
-    Cursor cur = cursor_seek(tab, ntensors, arena_offset + i * 8);
+    Cursor cur = cursor_seek(tab, ntensors, arena_offset + i * 8, wd_decay);
 
     for (; i < end; i += UNROLL * stride)
     {
@@ -308,7 +308,7 @@ __global__ void __launch_bounds__(BULK_THREADS, 1)
         }
     }
 
-    Cursor cur = cursor_seek(tab, ntensors, arena_offset + first_tile * BULK_TILE);
+    Cursor cur = cursor_seek(tab, ntensors, arena_offset + first_tile * BULK_TILE, wd_decay);
     long long done = 0;                         // tiles whose barrier this thread has passed
     for (long long k = 0; k < my_tiles; k++)
     {
@@ -335,9 +335,9 @@ __global__ void __launch_bounds__(BULK_THREADS, 1)
         const long long tile_begin = (first_tile + k * gridDim.x) * BULK_TILE;
         const unsigned cnt = tile_elems(k);
         const long long at0 = arena_offset + tile_begin;
-        cursor_advance(cur, tab, ntensors, at0);
+        cursor_advance(cur, tab, ntensors, at0, wd_decay);
         const bool uniform = at0 + cnt <= cur.next;
-        const float d_tile = tab.decay[cur.k] ? wd_decay : 1.0f;
+        const float d_tile = cur.factor;
 
         const unsigned q = threadIdx.x;         // quad of this thread: BULK_TILE / 4 == BULK_THREADS
         if (q * 4 < cnt)
@@ -346,8 +346,8 @@ __global__ void __launch_bounds__(BULK_THREADS, 1)
             if (!uniform)
             {
                 Cursor c2 = cur;
-                cursor_advance(c2, tab, ntensors, at0 + q * 4);
-                d = tab.decay[c2.k] ? wd_decay : 1.0f;
+                cursor_advance(c2, tab, ntensors, at0 + q * 4, wd_decay);
+                d = c2.factor;
             }
             float4 p4 = reinterpret_cast<float4 *>(sg.p)[q];
             float4 m4 = reinterpret_cast<float4 *>(sg.m)[q];

@@ -198,7 +198,7 @@ __global__ void __launch_bounds__(256)
     {
         return;
     }
-    Cursor cur = cursor_seek(tab, ntensors, arena_offset + i * 8);
+    Cursor cur = cursor_seek(tab, ntensors, arena_offset + i * 8, wd_decay);
     for (; i < n8; i += stride)
     {
         const uint4 gw = load_h8<0>(g16 + i);
