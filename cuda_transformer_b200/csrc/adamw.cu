@@ -22,7 +22,7 @@ __global__ void __launch_bounds__(P2_THREADS)
                            const b200amp_step_state *__restrict__ st, float b1, float b2, float eps)
 {
     __shared__ TensorTable tab;
-    table_load(tab, tensors, ntensors);
+    const int nruns = table_load(tab, tensors, ntensors);
     if (st->found_inf)
     {
         return;
@@ -40,7 +40,7 @@ __global__ void __launch_bounds__(P2_THREADS)
     {
         return;
     }
-    Cursor cur = cursor_seek(tab, ntensors, i * 4, wd_decay);
+    Cursor cur = cursor_seek(tab, nruns, i * 4, wd_decay);
     for (; i < n4; i += P2C_UNROLL * stride)
     {
         float4 g[P2C_UNROLL], p[P2C_UNROLL], mm[P2C_UNROLL], vv[P2C_UNROLL];
@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(P2_THREADS)
             const long long j = i + u * stride;
             if (u == 0 || j < n4)
             {
-                cursor_advance(cur, tab, ntensors, j * 4, wd_decay);
+                cursor_advance(cur, tab, nruns, j * 4, wd_decay);
                 const float d = cur.factor;
                 adamw_element(p[u].x, mm[u].x, vv[u].x, g[u].x * coef, w1, w2, b2, eps, d, step_size, bc2_sqrt);
                 adamw_element(p[u].y, mm[u].y, vv[u].y, g[u].y * coef, w1, w2, b2, eps, d, step_size, bc2_sqrt);

@@ -28,21 +28,59 @@ __device__ __forceinline__ void adamw_element(float &p, float &m, float &v, floa
     p = __fmaf_rn(-step_size, __fdiv_rn(m, denom), decayed);
 }
 
-// Tensor table in shared memory + the cursor over it.
+// Tensor table in shared memory + the cursor over it. Only a CHANGE of the decay flag matters
+// to the update, so neighbours with the same flag are merged while the table is loaded: the GPT
+// layout's 12 tensors per layer become 8 runs, and a thread that jumps over several small
+// tensors between two trips crosses fewer entries.
 struct TensorTable
 {
-    long long first[B200AMP_MAX_TENSORS];
-    unsigned char decay[B200AMP_MAX_TENSORS];
+    long long first[B200AMP_MAX_TENSORS];       // first element of each run
+    unsigned char decay[B200AMP_MAX_TENSORS];   // its flag
+    int warp_heads[32];                         // scratch of table_load
 };
 
-__device__ __forceinline__ void table_load(TensorTable &tab, const b200amp_tensor_info *tensors, int ntensors)
+// Every thread of the block must call this. Returns the number of runs (>= 1).
+__device__ __forceinline__ int table_load(TensorTable &tab, const b200amp_tensor_info *tensors, int ntensors)
 {
-    for (int k = threadIdx.x; k < ntensors; k += blockDim.x)
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int warps = (blockDim.x + 31) >> 5;
+    int base = 0;                               // runs found in earlier rounds (same value in every thread)
+    for (int k0 = 0; k0 < ntensors; k0 += blockDim.x)
     {
-        tab.first[k] = tensors[k].offset;
-        tab.decay[k] = tensors[k].decay ? 1 : 0;
+        const int k = k0 + threadIdx.x;
+        int flag = 0;
+        bool head = false;
+        long long offset = 0;
+        if (k < ntensors)
+        {
+            flag = tensors[k].decay ? 1 : 0;
+            offset = tensors[k].offset;
+            head = k == 0 || ((tensors[k - 1].decay ? 1 : 0) != flag);
+        }
+        const unsigned heads = __ballot_sync(0xffffffffu, head);
+        if (lane == 0)
+        {
+            tab.warp_heads[warp] = __popc(heads);
+        }
+        __syncthreads();
+        int before = base, total = base;
+        for (int w = 0; w < warps; w++)
+        {
+            const int c = tab.warp_heads[w];
+            before += w < warp ? c : 0;
+            total += c;
+        }
+        if (head)
+        {
+            const int slot = before + __popc(heads & ((1u << lane) - 1u));
+            tab.first[slot] = offset;
+            tab.decay[slot] = static_cast<unsigned char>(flag);
+        }
+        base = total;
+        __syncthreads();                        // warp_heads is rewritten by the next round; first/decay are read after
     }
-    __syncthreads();
+    return base;
 }
 
 struct Cursor
@@ -52,9 +90,16 @@ struct Cursor
     float factor;       // what a parameter of tensor k is multiplied by: the step's decay, or 1
 };
 
+// Reads of the table go through volatile accesses: they belong to the rare trip that crosses a
+// run's end, and must not be hoisted by the compiler into the trip that does not.
 __device__ __forceinline__ long long table_next(const TensorTable &tab, int ntensors, int k)
 {
-    return k + 1 < ntensors ? tab.first[k + 1] : LLONG_MAX;
+    return k + 1 < ntensors ? *static_cast<const volatile long long *>(&tab.first[k + 1]) : LLONG_MAX;
+}
+
+__device__ __forceinline__ float table_factor(const TensorTable &tab, int k, float wd_decay)
+{
+    return *static_cast<const volatile unsigned char *>(&tab.decay[k]) ? wd_decay : 1.0f;
 }
 
 __device__ __forceinline__ Cursor cursor_seek(const TensorTable &tab, int ntensors, long long at, float wd_decay)
@@ -75,7 +120,7 @@ __device__ __forceinline__ Cursor cursor_seek(const TensorTable &tab, int ntenso
     Cursor c;
     c.k = lo;
     c.next = table_next(tab, ntensors, lo);
-    c.factor = tab.decay[lo] ? wd_decay : 1.0f;
+    c.factor = table_factor(tab, lo, wd_decay);
     return c;
 }
 
@@ -91,7 +136,7 @@ __device__ __forceinline__ void cursor_advance(Cursor &c, const TensorTable &tab
             c.k += 1;
             c.next = table_next(tab, ntensors, c.k);
         } while (at >= c.next);
-        c.factor = tab.decay[c.k] ? wd_decay : 1.0f;
+        c.factor = table_factor(tab, c.k, wd_decay);
     }
 }
 

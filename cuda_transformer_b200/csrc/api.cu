@@ -62,7 +62,7 @@ int sm_count()
 
 Tunables &tunables()
 {
-    static Tunables t = {4, 2, 1, 1, 256, 0, 0, 6, 8, 0};   // measured best on B200 at the 1.3 B arena
+    static Tunables t = {4, 2, 1, 256, 0, 6, 8, 0};   // measured best on B200 at the 1.3 B arena
     return t;
 }
 
@@ -76,10 +76,8 @@ struct Knob
 static const Knob KNOBS[] = {
     {"pass1_blocks_per_sm", &Tunables::pass1_blocks_per_sm, 1, 32},
     {"pass2_blocks_per_sm", &Tunables::pass2_blocks_per_sm, 1, 32},
-    {"pass2_unroll", &Tunables::pass2_unroll, 1, 4},
     {"pass2_store_hint", &Tunables::pass2_store_hint, 0, 1},
     {"pass2_threads", &Tunables::pass2_threads, 256, 1024},
-    {"pass2_partition", &Tunables::pass2_partition, 0, 1},
     {"pass2_variant", &Tunables::pass2_variant, 0, 1},
     {"pass2_stages", &Tunables::pass2_stages, 3, 7},
     {"rs_blocks_per_sm", &Tunables::rs_blocks_per_sm, 1, 32},

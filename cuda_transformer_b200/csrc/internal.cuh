@@ -25,10 +25,8 @@ struct Tunables
 {
     int pass1_blocks_per_sm;    // resident CTAs per SM asked for in pass 1
     int pass2_blocks_per_sm;    // same, pass 2
-    int pass2_unroll;           // 8-element groups per thread per trip: 1, 2 or 4
     int pass2_store_hint;       // 0: plain stores, 1: st.global.cs (streaming)
     int pass2_threads;          // threads per CTA of the registers-only kernel: 256, 512 or 1024
-    int pass2_partition;        // 0: the grid sweeps the arena together, 1: one contiguous range per CTA
     int pass2_variant;          // 0: registers-only kernel, 1: shared-memory staged kernel (bulk async copies)
     int pass2_stages;           // ring depth of the staged kernel: 3..7 (28 KB each)
     int rs_blocks_per_sm;       // resident CTAs per SM of the fused reduce-scatter + pass 1

@@ -179,7 +179,7 @@ __global__ void __launch_bounds__(256)
 {
     constexpr int THREADS = 256;
     __shared__ TensorTable tab;
-    table_load(tab, tensors, ntensors);
+    const int nruns = table_load(tab, tensors, ntensors);
     if (st->found_inf)
     {
         return;                                 // skipped step: no rank's arena is touched
@@ -198,7 +198,7 @@ __global__ void __launch_bounds__(256)
     {
         return;
     }
-    Cursor cur = cursor_seek(tab, ntensors, arena_offset + i * 8, wd_decay);
+    Cursor cur = cursor_seek(tab, nruns, arena_offset + i * 8, wd_decay);
     for (; i < n8; i += stride)
     {
         const uint4 gw = load_h8<0>(g16 + i);
@@ -206,7 +206,7 @@ __global__ void __launch_bounds__(256)
         Float8 mm = load8<0>(m + i * 8);
         Float8 vv = load8<0>(v + i * 8);
         float d_lo, d_hi;
-        group_decay(cur, tab, ntensors, arena_offset + i * 8, wd_decay, d_lo, d_hi);
+        group_decay(cur, tab, nruns, arena_offset + i * 8, wd_decay, d_lo, d_hi);
         const uint32_t words[4] = {gw.x, gw.y, gw.z, gw.w};
 #pragma unroll
         for (int k = 0; k < 4; k++)

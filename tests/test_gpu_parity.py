@@ -367,12 +367,12 @@ def test_result_does_not_depend_on_launch_shape(G):
     bits = (rng.standard_normal(n) * 1e-3 * 65536.0).astype(np.float16).view(np.uint16)
     table = [(0, 1000, 0), (1000, n - 1000, 1)]
     results = []
-    base = dict(pass1_blocks_per_sm=8, pass2_blocks_per_sm=4, pass2_unroll=1, pass2_store_hint=0, pass2_threads=256,
-                pass2_partition=0, pass2_variant=0, pass2_stages=6)
+    base = dict(pass1_blocks_per_sm=8, pass2_blocks_per_sm=4, pass2_store_hint=0, pass2_threads=256,
+                pass2_variant=0, pass2_stages=6)
     knobs = [base,
-             dict(base, pass1_blocks_per_sm=1, pass2_blocks_per_sm=1, pass2_unroll=2, pass2_store_hint=1),
-             dict(base, pass1_blocks_per_sm=3, pass2_blocks_per_sm=7, pass2_unroll=4, pass2_partition=1),
-             dict(base, pass2_threads=512, pass2_unroll=2, pass2_blocks_per_sm=1, pass2_partition=1),
+             dict(base, pass1_blocks_per_sm=1, pass2_blocks_per_sm=1, pass2_store_hint=1),
+             dict(base, pass1_blocks_per_sm=3, pass2_blocks_per_sm=7),
+             dict(base, pass2_threads=512, pass2_blocks_per_sm=1, pass2_store_hint=1),
              dict(base, pass2_threads=1024, pass2_blocks_per_sm=1),
              dict(base, pass2_variant=1, pass2_stages=6),
              dict(base, pass2_variant=1, pass2_stages=3)]
