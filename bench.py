@@ -136,7 +136,15 @@ def cpu_sample_shapes(name: str):
 
 def run_cpu_reference(workload: str, steps: int, warmup: int) -> dict:
     """The reference's PyTorch CPU path (reference/train.py:147-153 order) on the host cores."""
+    import torch
     from oracle.torch_ref import time_cpu_step
+    # every host core the process may use: torchrun exports OMP_NUM_THREADS=1, which would
+    # otherwise pin the CPU path to one thread
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count() or 1
+    torch.set_num_threads(max(1, cores))
     shapes, what = cpu_sample_shapes(workload)
     r = time_cpu_step(shapes, steps=max(1, steps), warmup=max(1, warmup), loss_scale=32768.0)
     gps = r["params"] / r["seconds_per_step"] / 1e9
@@ -191,8 +199,22 @@ def run_gpu(args) -> dict:
         step_fn = opt.optimizer_step
     else:
         fused = args.collectives == "fused"
-        make = amp.FusedZero1Optimizer if fused else amp.ShardedAmpOptimizer
-        opt = make(slots, cfg, eps=1e-8, loss_scale=loss_scale, device=dev)
+        fused_note = None
+        if fused:
+            # symmetric memory needs peer access between all ranks' GPUs; where the box cannot give
+            # it, every rank falls back together to NCCL around the passes (and the line says so)
+            try:
+                opt = amp.FusedZero1Optimizer(slots, cfg, eps=1e-8, loss_scale=loss_scale, device=dev)
+                ok = torch.ones(1, device=dev)
+            except Exception as e:      # noqa: BLE001
+                opt, ok, fused_note = None, torch.zeros(1, device=dev), f"{type(e).__name__}: {e}"[:200]
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if float(ok.item()) < 1.0:
+                fused = False
+                opt = None
+                torch.cuda.empty_cache()
+        if not fused:
+            opt = amp.ShardedAmpOptimizer(slots, cfg, eps=1e-8, loss_scale=loss_scale, device=dev)
         # the same master values as the 1-GPU run would hold in this slice would need the whole
         # stream; a per-rank seed gives the same distribution, which is all the timing needs
         fill_normal_(opt.master, 0.02, seed=100 + rank)
@@ -320,6 +342,8 @@ def run_gpu(args) -> dict:
         phases["all_gather_gbs"] = coll_bytes / (phases["all_gather_ms"] * 1e-3) / 1e9
         phases["nvlink_peak_gbs"] = NVLINK_MEASURED_GBS
         phases["collectives"] = "NCCL reduce_scatter_tensor(AVG) / all_gather_into_tensor around the passes"
+        if args.collectives == "fused":
+            phases["collectives"] += " (fused path unavailable on this box: %s)" % (fused_note or "a peer rank failed")
     st = opt.read_state()
     if st.skipped != 0:
         raise SystemExit("a timed step was skipped: the timing would count 2 B/param steps")
@@ -347,7 +371,6 @@ def run_gpu(args) -> dict:
     e1.record()
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
-    launches += 0       # e2e launches are outside the timed region that `value` reports
 
     if world > 1:
         dist.barrier()
