@@ -29,6 +29,7 @@ struct Tunables
     int pass2_threads;          // threads per CTA of the registers-only kernel: 256, 512 or 1024
     int pass2_variant;          // 0: registers-only kernel, 1: shared-memory staged kernel (bulk async copies)
     int pass2_stages;           // ring depth of the staged kernel: 3..7 (28 KB each)
+    int pass2_test_starve;      // test hook of the staged kernel: 1 makes one barrier wait run out (see pass2.cu)
     int rs_blocks_per_sm;       // resident CTAs per SM of the fused reduce-scatter + pass 1
     int ag_blocks_per_sm;       // resident CTAs per SM of the fused pass 2 + all-gather, 0 = by rank count
 };

@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(THREADS)
 constexpr int BULK_TILE = 2048;                 // elements per tile
 constexpr int BULK_THREADS = 512;               // one quad (4 elements) per thread per tile
 constexpr int BULK_MAX_STAGES = 7;
-constexpr unsigned BULK_WAIT_LIMIT = 1u << 22;  // polls of one barrier before the kernel gives up
+constexpr unsigned BULK_WAIT_LIMIT = 1u << 20;  // polls of one barrier before the kernel gives up (a fraction of a second)
 
 struct __align__(128) BulkStage
 {
@@ -225,7 +225,8 @@ __global__ void __launch_bounds__(BULK_THREADS, 1)
     pass2_bulk_kernel(float *__restrict__ master, float *__restrict__ m, float *__restrict__ v,
                       const __half *__restrict__ g16, __half *__restrict__ w16, long long n, long long arena_offset,
                       const b200amp_tensor_info *__restrict__ tensors, int ntensors,
-                      const b200amp_step_state *__restrict__ st, float b1, float b2, float eps, int stages)
+                      const b200amp_step_state *__restrict__ st, float b1, float b2, float eps, int stages,
+                      int starve)
 {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     BulkStage *stage = reinterpret_cast<BulkStage *>(smem_raw);
@@ -278,7 +279,10 @@ __global__ void __launch_bounds__(BULK_THREADS, 1)
         const unsigned cnt = tile_elems(k);
         BulkStage &sg = stage[k % stages];
         uint64_t *bar = &full[k % stages];
-        mbar_expect_tx(bar, cnt * 14u);
+        // starve (test hook): CTA 0 announces 16 bytes that never come for its second tile, so that
+        // barrier's wait runs into its limit and the give-up path below is exercised
+        const unsigned never = (starve != 0 && blockIdx.x == 0 && k == 1) ? 16u : 0u;
+        mbar_expect_tx(bar, cnt * 14u + never);
         bulk_load(sg.g, g16 + begin, cnt * 2u, bar);
         bulk_load(sg.p, master + begin, cnt * 4u, bar);
         bulk_load(sg.m, m + begin, cnt * 4u, bar);
@@ -375,7 +379,9 @@ __global__ void __launch_bounds__(BULK_THREADS, 1)
             g_bulk_timeout = 1;
             // loads already issued still target this CTA's shared memory: give each one more bounded
             // wait before the memory is handed back
-            long long issued = done + lookahead < my_tiles ? done + lookahead : my_tiles;
+            // tiles 0 .. done + lookahead have been requested (the trip that gave up had already
+            // asked for its look-ahead tile)
+            long long issued = done + lookahead + 1 < my_tiles ? done + lookahead + 1 : my_tiles;
             for (long long k = done; k < issued; k++)
             {
                 mbar_wait(&full[k % stages], static_cast<unsigned>((k / stages) & 1));
@@ -480,7 +486,7 @@ extern "C" B200AMP_API int b200amp_pass2_f16(float *master, float *m, float *v, 
         }
         pass2_bulk_kernel<<<grid, BULK_THREADS, bulk_smem_bytes(stages), stream>>>(
             master, m, v, static_cast<const __half *>(grads16), static_cast<__half *>(weights16), n, arena_offset,
-            tensors, ntensors, st, beta1, beta2, eps, stages);
+            tensors, ntensors, st, beta1, beta2, eps, stages, t.pass2_test_starve);
         B200AMP_LAUNCHED();
         return B200AMP_OK;
     }
@@ -514,13 +520,18 @@ extern "C" B200AMP_API int b200amp_pass2_f16(float *master, float *m, float *v, 
     return B200AMP_OK;
 }
 
-// 1 if a shared-memory staged launch on the current device gave up waiting for a copy since
-// the library was loaded. Synchronises the device.
+// 1 if a shared-memory staged launch on the current device gave up waiting for a copy since the
+// last call (the flag is cleared by reading it). Synchronises the device.
 extern "C" B200AMP_API int b200amp_device_error(int *out)
 {
     B200AMP_REQUIRE(out != nullptr, "device_error: out is null");
     int flag = 0;
     B200AMP_CUDA(cudaMemcpyFromSymbol(&flag, g_bulk_timeout, sizeof(int)));
+    if (flag != 0)
+    {
+        const int zero = 0;
+        B200AMP_CUDA(cudaMemcpyToSymbol(g_bulk_timeout, &zero, sizeof(int)));
+    }
     *out = flag;
     return B200AMP_OK;
 }

@@ -263,8 +263,9 @@ B200AMP_API int b200amp_graph_destroy(b200amp_graph *g);
  * reference's surface. Unknown keys return B200AMP_ERR_ARG. Results never depend on them. */
 B200AMP_API int b200amp_tune_set(const char *key, int value);
 B200AMP_API int b200amp_tune_get(const char *key, int *value);
-/* *out = 1 if a kernel of this library on the current device ever gave up a bounded wait (a
- * bulk copy that never completed), else 0. Synchronises the device. */
+/* *out = 1 if a kernel of this library on the current device gave up a bounded wait (a bulk
+ * copy that never completed) since the last call, else 0; reading clears the flag.
+ * Synchronises the device. */
 B200AMP_API int b200amp_device_error(int *out);
 /* Kernel launches enqueued by this library on the calling process so far. */
 B200AMP_API long long b200amp_launch_count(void);

@@ -608,3 +608,51 @@ def test_native_path_matches_the_reference_kernels(G):
         assert H.rel_err(y, x) <= H.STATE_TOL
     assert H.half_ulp_distance(ht[3], hm[3]) <= 1
     assert mine.read_state().skipped == 1 and mine.read_state().adam_t == 9
+
+
+def test_staged_kernel_gives_up_a_starved_wait_and_reports_it(G):
+    """Failure detection without a fault: the staged kernel's barrier waits are bounded. With the
+    test hook one CTA announces bytes that never arrive; its wait must run out (well under a
+    second), the kernel must return, b200amp_device_error must report it once, and the context
+    must stay usable."""
+    import time
+    from cuda_transformer_b200 import _lib, amp
+    lib = _lib.load()
+    n = 148 * 2048 * 6
+    rng = np.random.default_rng(13)
+    init = (rng.standard_normal(n) * 0.02).astype(np.float32)
+    bits = (rng.standard_normal(n) * 1e-3 * 65536.0).astype(np.float16).view(np.uint16)
+    flag = C.c_int(-1)
+    _lib.check(lib.b200amp_device_error(C.byref(flag)))                 # clear anything older
+    g = G.GpuStep(init, [(0, n, 1)], sched(amp), loss_scale=65536.0)
+    g.set_grads16(bits)
+    try:
+        _lib.check(lib.b200amp_tune_set(b"pass2_variant", 1))
+        _lib.check(lib.b200amp_tune_set(b"pass2_test_starve", 1))
+        t0 = time.perf_counter()
+        g.step_f16()
+        torch.cuda.synchronize()
+        waited = time.perf_counter() - t0
+    finally:
+        lib.b200amp_tune_set(b"pass2_test_starve", 0)
+        lib.b200amp_tune_set(b"pass2_variant", 0)
+    assert waited < 10.0, f"the bounded wait took {waited:.1f} s"
+    _lib.check(lib.b200amp_device_error(C.byref(flag)))
+    assert flag.value == 1, "the starved wait was not reported"
+    _lib.check(lib.b200amp_device_error(C.byref(flag)))
+    assert flag.value == 0, "reading the flag clears it"
+    # the context is intact: a fresh optimizer steps and matches the registers-only kernel
+    a = G.GpuStep(init, [(0, n, 1)], sched(amp), loss_scale=65536.0)
+    a.set_grads16(bits)
+    a.step_f16()
+    _lib.check(lib.b200amp_tune_set(b"pass2_variant", 1))
+    try:
+        b = G.GpuStep(init, [(0, n, 1)], sched(amp), loss_scale=65536.0)
+        b.set_grads16(bits)
+        b.step_f16()
+        torch.cuda.synchronize()
+    finally:
+        lib.b200amp_tune_set(b"pass2_variant", 0)
+    assert all(np.array_equal(x, y) for x, y in zip(a.host(), b.host()))
+    _lib.check(lib.b200amp_device_error(C.byref(flag)))
+    assert flag.value == 0
