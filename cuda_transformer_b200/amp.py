@@ -236,8 +236,7 @@ class AmpOptimizer:
     """
 
     def __init__(self, slots: List[ParamSlot], cfg: ScheduleConfig, eps: float = 1e-8,
-                 loss_scale: float = 65536.0, history_len: int = 256, device="cuda:0",
-                 extra_tensors: Sequence[Tuple[int, int, int]] = ()):
+                 loss_scale: float = 65536.0, history_len: int = 256, device="cuda:0"):
         self.lib = _lib.load()
         check(self._with_device(device, self.lib.b200amp_device_check))
         self.device = torch.device(device)
@@ -247,8 +246,8 @@ class AmpOptimizer:
         self.sched = cfg
         self.beta1, self.beta2, self.eps = cfg.beta1, cfg.beta2, eps
         self.history_len = history_len
-        table = list(tensor_table(slots)) + list(extra_tensors)
-        if self.n > self.n_params and not extra_tensors:
+        table = list(tensor_table(slots))
+        if self.n > self.n_params:
             table.append((self.n_params, self.n - self.n_params, 0))       # zero padding: never decayed
         self.ntensors = len(table)
         with torch.cuda.device(self.device):

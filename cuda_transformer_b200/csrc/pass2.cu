@@ -25,6 +25,8 @@
 // The decay flag comes from a cursor into the tensor table that advances as positions
 // grow, instead of a binary search per vector (the search runs once per thread).
 
+#include <mutex>
+
 #include "adamw_math.cuh"
 
 namespace b200amp
@@ -420,6 +422,8 @@ static int prepare_bulk(int stages)
     // opt in to more than 48 KB of dynamic shared memory, once per device and stage count
     constexpr int MAX_DEVICES = 64;
     static int prepared[MAX_DEVICES] = {};
+    static std::mutex guard;
+    std::lock_guard<std::mutex> hold(guard);
     int dev = 0;
     B200AMP_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= MAX_DEVICES)

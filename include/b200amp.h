@@ -260,7 +260,8 @@ B200AMP_API int b200amp_graph_destroy(b200amp_graph *g);
 
 /* ---------------------------------------------------------------- tuning hooks
  * Launch-shape knobs for measurement (blocks per SM, variant); not part of the
- * reference's surface. Unknown keys return B200AMP_ERR_ARG. Results never depend on them. */
+ * reference's surface. Unknown keys return B200AMP_ERR_ARG. Results never depend on them.
+ * Process-wide and unsynchronised: set them before other threads launch work. */
 B200AMP_API int b200amp_tune_set(const char *key, int value);
 B200AMP_API int b200amp_tune_get(const char *key, int *value);
 /* *out = 1 if a kernel of this library on the current device gave up a bounded wait (a bulk
