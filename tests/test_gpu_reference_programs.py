@@ -51,7 +51,7 @@ def test_reference_program_passes_on_the_library(prog, tmp_path):
     bins, dump = _programs()
     stock, stock_failed, _ = _run(bins[f"{prog}_stock"], dump, tmp_path)
     ours, ours_failed, ours_ok = _run(bins[f"{prog}_b200amp"], dump, tmp_path)
-    out_dir = os.path.join(REPO, "gpurun_out")
+    out_dir = os.environ.get("B200AMP_TEST_LOG_DIR") or str(tmp_path)     # keep the programs' full output
     os.makedirs(out_dir, exist_ok=True)
     for tag, proc in (("stock", stock), ("b200amp", ours)):
         with open(os.path.join(out_dir, f"ref_{prog}_{tag}.log"), "w") as f:
