@@ -70,6 +70,7 @@ PROTOTYPES = {
     "b200amp_workspace_init": (_I, [_P, _P]),
     "b200amp_pass1_f16": (_I, [_P, _LL, _P, _P, _P]),
     "b200amp_pass1_f16_static": (_I, [_P, _LL, _P, _P, _P]),
+    "b200amp_cast_pass1_f32": (_I, [_P, _P, _LL, _I, _P, _P, C.POINTER(ScheduleConfig), _P, _I, _P]),
     "b200amp_finalize_sums": (_I, [_P, _P, _I, C.POINTER(ScheduleConfig), _P, _I, _P]),
     "b200amp_pass1_finalize_f16": (_I, [_P, _LL, _P, _P, C.POINTER(ScheduleConfig), _P, _I, _P]),
     "b200amp_pass2_f16": (_I, [_P, _P, _P, _P, _P, _LL, _LL, _P, _I, _P, _F, _F, _F, _P]),

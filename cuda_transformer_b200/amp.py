@@ -34,7 +34,7 @@ __all__ = [
     "StepState", "ScheduleConfig", "TensorInfo", "B200AmpError",
     "initial_state", "begin_step", "unscale_and_norm", "finalize_step", "adamw_multi", "lr_on_gpu",
     "cast_to_x", "CudaGraph", "AmpOptimizer", "Zero1Step", "ShardedAmpOptimizer", "make_schedule",
-    "pass1_f16", "pass1_f16_static", "pass1_finalize_f16", "rs_pass1_f16", "pass2_ag_f16", "FusedZero1Optimizer", "finalize_sums", "pass2_f16", "step_f16",
+    "pass1_f16", "pass1_f16_static", "cast_pass1_f32", "pass1_finalize_f16", "rs_pass1_f16", "pass2_ag_f16", "FusedZero1Optimizer", "finalize_sums", "pass2_f16", "step_f16",
 ]
 
 
@@ -124,6 +124,15 @@ def pass1_f16_static(grads16, n: int, st, sums_out, stream=None) -> None:
     """Pass 1 on the library's own scratch: for callers that cannot allocate device memory.
     sums_out: device memory for two doubles {sum of squares, flag}. See include/b200amp.h."""
     check(_lib.load().b200amp_pass1_f16_static(_ptr(grads16), n, _ptr(st), _ptr(sums_out), _stream(stream)))
+
+
+def cast_pass1_f32(grads32, grads16, n: int, clear_source: bool, st, workspace, cfg: Optional[ScheduleConfig] = None,
+                   history=None, history_len: int = 0, stream=None) -> None:
+    """fp32 loss-scaled gradients -> fp16 arena + pass 1 (+ finalize when cfg is given) in one sweep;
+    clear_source zeroes the fp32 arena behind it (the reference's per-step grads.zero)."""
+    check(_lib.load().b200amp_cast_pass1_f32(_ptr(grads32), _ptr(grads16), n, 1 if clear_source else 0, _ptr(st),
+                                             _ptr(workspace), C.byref(cfg) if cfg is not None else None,
+                                             _ptr(history), history_len, _stream(stream)))
 
 
 def pass1_finalize_f16(grads16, n: int, st, workspace, cfg: ScheduleConfig, history=None, history_len: int = 0,

@@ -189,6 +189,19 @@ B200AMP_API int b200amp_pass1_f16(const void *grads16, long long n, const b200am
 B200AMP_API int b200amp_pass1_f16_static(const void *grads16, long long n, const b200amp_step_state *st,
                                          double *sums_out, b200amp_stream s);
 
+/* The step before the path: the bridge from the reference's fp32 gradient arena to the fp16
+ * arena. grads32[n] holds loss-scaled fp32 gradients as the reference's backward pass leaves
+ * them (cuda/gpt_fast.cu:455-457, cuda/kernels/gemm_common.cuh:11). One sweep writes
+ * grads16 = fp16(grads32) (round to nearest even; out-of-range values become inf and skip the
+ * step), computes pass 1 on exactly those fp16 values (workspace as b200amp_pass1_f16), and,
+ * if clear_source != 0, zeroes grads32 in place, which replaces the reference's per-step
+ * grads.zero memset. With cfg != null the finalize runs in the same launch (cfg, history and
+ * history_len as b200amp_pass1_finalize_f16); with cfg == null only {sum, flag} are
+ * published, as b200amp_pass1_f16 does. n % 8 == 0; grads32 32-byte, grads16 16-byte aligned. */
+B200AMP_API int b200amp_cast_pass1_f32(float *grads32, void *grads16, long long n, int clear_source,
+                                       b200amp_step_state *st, void *workspace, const b200amp_schedule *cfg,
+                                       b200amp_step_state *history, int history_len, b200amp_stream s);
+
 /* Finalize from nranks pairs {sum of squares, flag} laid out rank after rank
  * (device memory, e.g. the output of an all-gather of every rank's first 16
  * workspace bytes). Pairs are added in rank order, so every rank computes the

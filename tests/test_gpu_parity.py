@@ -656,3 +656,51 @@ def test_staged_kernel_gives_up_a_starved_wait_and_reports_it(G):
     assert all(np.array_equal(x, y) for x, y in zip(a.host(), b.host()))
     _lib.check(lib.b200amp_device_error(C.byref(flag)))
     assert flag.value == 0
+
+
+def test_fp32_gradient_bridge_matches_cast_then_pass1(G):
+    """b200amp_cast_pass1_f32: the reference's fp32 loss-scaled gradient arena -> fp16 arena + pass 1
+    (+ finalize) in one sweep, optionally clearing the fp32 arena. Must equal: round to fp16, then the
+    native pass 1 / step on that fp16 arena, bit for bit; an fp32 value beyond the fp16 range becomes
+    inf and skips the step."""
+    from cuda_transformer_b200 import _lib, amp
+    n = (1 << 21) + 8 * 77
+    rng = np.random.default_rng(31)
+    init = (rng.standard_normal(n) * 0.02).astype(np.float32)
+    table = [(0, 4096, 0), (4096, n - 4096, 1)]
+    for trial, poison in enumerate((False, True)):
+        g32_host = (rng.standard_normal(n) * 1e-3 * 65536.0).astype(np.float32)
+        if poison:
+            g32_host[n // 3] = 1.0e6                      # finite in fp32, inf in fp16
+        want16 = g32_host.astype(np.float16)
+        # (a) reference flow: fp16 arena given, native step
+        a = G.GpuStep(init, table, sched(amp), loss_scale=65536.0)
+        a.set_grads16(want16.view(np.uint16))
+        a.step_f16()
+        # (b) bridge with the finalize inside, then pass 2
+        b = G.GpuStep(init, table, sched(amp), loss_scale=65536.0)
+        g32 = G.to_dev(g32_host)
+        amp.cast_pass1_f32(g32, b.grads16, n, True, b.state, b.workspace, b.cfg, b.history, b.history_len)
+        amp.pass2_f16(b.master, b.m, b.v, b.grads16, b.weights16, n, 0, b.tensors, b.ntensors, b.state,
+                      b.cfg.beta1, b.cfg.beta2, b.eps)
+        torch.cuda.synchronize()
+        assert np.array_equal(H.f16_bits(b.grads16.cpu()), want16.view(np.uint16))
+        assert not g32.any(), "clear_source must leave zeros in the fp32 arena"
+        assert bytes(a.read_state()) == bytes(b.read_state())
+        assert all(np.array_equal(x, y) for x, y in zip(a.host(), b.host()))
+        assert b.read_state().found_inf == (1 if poison else 0)
+        # (c) without the finalize and without clearing: only {sum, flag}, source untouched
+        c = G.GpuStep(init, table, sched(amp), loss_scale=65536.0)
+        g32 = G.to_dev(g32_host)
+        amp.cast_pass1_f32(g32, c.grads16, n, False, c.state, c.workspace)
+        ws_ref = torch.zeros_like(c.workspace)
+        amp.pass1_f16(c.grads16, n, c.state, ws_ref)
+        torch.cuda.synchronize()
+        got = c.workspace[:16].view(torch.float64).cpu().numpy()
+        ref = ws_ref[:16].view(torch.float64).cpu().numpy()
+        assert got[1] == ref[1] == (1.0 if poison else 0.0)
+        assert (got[0] == ref[0]) or (np.isinf(got[0]) and np.isinf(ref[0]))
+        assert np.array_equal(g32.cpu().numpy(), g32_host)
+        assert c.read_state().step == 0
+    with pytest.raises(amp.B200AmpError):
+        amp.cast_pass1_f32(g32, c.grads16, n - 4, False, c.state, c.workspace)
