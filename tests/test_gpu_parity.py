@@ -704,3 +704,37 @@ def test_fp32_gradient_bridge_matches_cast_then_pass1(G):
         assert c.read_state().step == 0
     with pytest.raises(amp.B200AmpError):
         amp.cast_pass1_f32(g32, c.grads16, n - 4, False, c.state, c.workspace)
+
+
+def test_compat_adamw_wide_and_narrow_forms_agree(G, O):
+    """b200amp_adamw_multi_f32 uses 256-bit accesses when n % 8 == 0 and the arrays are 32-byte
+    aligned, and the reference's 4-element granularity otherwise. Same arena through both forms
+    (the narrow one by starting 4 elements in): same bits, and both match the oracle."""
+    from cuda_transformer_b200 import amp
+    n = 8 * 4099
+    rng = np.random.default_rng(41)
+    init = (rng.standard_normal(n + 8) * 0.5).astype(np.float32)
+    g = (rng.standard_normal(n + 8) * 1e-3).astype(np.float32)
+    table = [(0, 1028, 1), (1028, 2052, 0), (3080, n + 8 - 3080, 1)]
+    kw = dict(weight_decay=0.3, lr=1e-2, min_lr=1e-2, grad_clip=1e30)
+    wide = G.GpuStep(init[:n], table, sched(amp, **kw), loss_scale=1.0)
+    wide.step_f32(g[:n])
+    ora = O.OracleStep(init[:n], table, sched(O, **kw), loss_scale=1.0)
+    ora.step_f32(g[:n])
+    compare_arrays(wide, ora)
+    # the narrow form: n - 4 elements starting at element 4 (16-byte aligned only), table shifted by 4
+    full = G.GpuStep(init[:n], table, sched(amp, **kw), loss_scale=1.0)
+    shifted = [(0, 1024, 1), (1024, 2052, 0), (3076, n - 4 - 3076, 1)]
+    tab_dev = G.table_dev(shifted)
+    g_dev = G.to_dev(g[:n])
+    amp.begin_step(full.state)
+    amp.unscale_and_norm(g_dev, n, full.state, full.partial)
+    amp.finalize_step(full.state, full.partial, full.cfg, full.history, full.history_len)
+    m4 = n - 4
+    amp.adamw_multi(full.master.data_ptr() + 16, full.weights16.data_ptr() + 8, g_dev.data_ptr() + 16,
+                    full.m.data_ptr() + 16, full.v.data_ptr() + 16, m4, tab_dev, len(shifted), full.state,
+                    full.cfg.beta1, full.cfg.beta2, full.eps)
+    torch.cuda.synchronize()
+    for a, b in zip(wide.host(), full.host()):
+        assert np.array_equal(a[4:], b[4:])
+    assert np.array_equal(full.host()[0][:4], init[:4])         # the first quad was outside the narrow call
