@@ -30,6 +30,7 @@ OBJ = os.path.join(OUT, "obj")
 BIN = os.path.join(OUT, "bin")
 DUMP = os.path.join(OUT, "data", "debug.bin")
 ROUNDTRIP = os.path.join(BIN, "ckpt_roundtrip")
+WEIGHTS_ROUNDTRIP = os.path.join(BIN, "weights_roundtrip")
 DEFAULT_REF = "/root/reference"
 REPLACED = ("kernels/scaler.cu", "kernels/adamw_multi.cu", "graph.cu")
 PROGRAMS = ("test_fast", "test_checkpoint")
@@ -120,6 +121,14 @@ def build(ref_root: str = DEFAULT_REF, jobs: int = 8):
     rt_obj = os.path.join(OBJ, "ckpt_roundtrip.o")
     _compile(os.path.join(HERE, "ckpt_roundtrip.cu"), rt_obj, includes)
     cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-o", ROUNDTRIP, rt_obj] + \
+        [os.path.join(OBJ, r[:-3] + ".o") for r in common]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("link failed: " + " ".join(cmd) + "\n" + proc.stderr[-4000:])
+    # weights_roundtrip: the same for weights.bin
+    wr_obj = os.path.join(OBJ, "weights_roundtrip.o")
+    _compile(os.path.join(HERE, "weights_roundtrip.cu"), wr_obj, includes)
+    cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-o", WEIGHTS_ROUNDTRIP, wr_obj] + \
         [os.path.join(OBJ, r[:-3] + ".o") for r in common]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
