@@ -163,4 +163,55 @@ __device__ __forceinline__ void group_decay(Cursor &c, const TensorTable &tab, i
     }
 }
 
+// ---------------------------------------------------------------- one group of pass 2
+
+struct StepFactors          // the step's scalars, read once per thread
+{
+    float coef, step_size, bc2_sqrt, inv, w1, w2, b2, eps;
+};
+
+__device__ __forceinline__ StepFactors step_factors(const b200amp_step_state *st, float b1, float b2, float eps)
+{
+    return {st->clip_coef, st->step_size, st->bc2_sqrt, st->inv_scale, 1.0f - b1, 1.0f - b2, b2, eps};
+}
+
+// One 8-element group at vector index j of the native step: unscale + clip + AdamW on master, m,
+// v in place, then emit(j, the 8 new parameters as fp16) for the caller to store wherever the
+// fp16 copy lives (one arena, or every rank's). The four loads are issued first; the decay
+// factors of the group's two quads are looked up (decay(d_lo, d_hi)) while they are in flight.
+template <int ST, class DecayFn, class EmitFn>
+__device__ __forceinline__ void update_group(float *__restrict__ master, float *__restrict__ m, float *__restrict__ v,
+                                             const uint4 *__restrict__ g16, int j, DecayFn decay, EmitFn emit,
+                                             const StepFactors &f)
+{
+    const size_t e = static_cast<size_t>(j) * 8;    // first element of the group
+    const uint4 gw = load_h8<0>(g16 + j);
+    Float8 pp = load8<0>(master + e);
+    Float8 mm = load8<0>(m + e);
+    Float8 vv = load8<0>(v + e);
+    float d_lo, d_hi;
+    decay(d_lo, d_hi);
+    const uint32_t words[4] = {gw.x, gw.y, gw.z, gw.w};
+#pragma unroll
+    for (int k = 0; k < 4; k++)
+    {
+        const float2 h = half2_bits_to_float2(words[k]);
+        const float d = k < 2 ? d_lo : d_hi;
+        // (g16 * inv) is the unscaled fp32 gradient of the reference, then * clip
+        adamw_element(pp.v[2 * k], mm.v[2 * k], vv.v[2 * k], (h.x * f.inv) * f.coef, f.w1, f.w2, f.b2, f.eps, d,
+                      f.step_size, f.bc2_sqrt);
+        adamw_element(pp.v[2 * k + 1], mm.v[2 * k + 1], vv.v[2 * k + 1], (h.y * f.inv) * f.coef, f.w1, f.w2, f.b2,
+                      f.eps, d, f.step_size, f.bc2_sqrt);
+    }
+    store8<ST>(master + e, pp);
+    store8<ST>(m + e, mm);
+    store8<ST>(v + e, vv);
+    uint4 out;
+    out.x = float2_to_half2_bits(pp.v[0], pp.v[1]);
+    out.y = float2_to_half2_bits(pp.v[2], pp.v[3]);
+    out.z = float2_to_half2_bits(pp.v[4], pp.v[5]);
+    out.w = float2_to_half2_bits(pp.v[6], pp.v[7]);
+    emit(j, out);
+}
+
 } // namespace b200amp

@@ -34,51 +34,6 @@ namespace b200amp
 
 // ---------------------------------------------------------------- registers-only kernel
 
-struct StepFactors          // the step's scalars, read once per thread
-{
-    float coef, step_size, bc2_sqrt, inv, w1, w2, b2, eps;
-};
-
-// One 8-element group at vector index j. The four loads are issued first; the decay factors of
-// the group's two quads are looked up (decay(d_lo, d_hi)) while they are in flight.
-template <int ST, class DecayFn>
-__device__ __forceinline__ void update_group(float *__restrict__ master, float *__restrict__ m, float *__restrict__ v,
-                                             const uint4 *__restrict__ g16, uint4 *__restrict__ w16, int j,
-                                             DecayFn decay, const StepFactors &f)
-{
-    const size_t e = static_cast<size_t>(j) * 8;    // first element of the group
-    const uint4 gw = load_h8<0>(g16 + j);
-    Float8 pp = load8<0>(master + e);
-    Float8 mm = load8<0>(m + e);
-    Float8 vv = load8<0>(v + e);
-    float d_lo, d_hi;
-    decay(d_lo, d_hi);
-    const uint32_t words[4] = {gw.x, gw.y, gw.z, gw.w};
-#pragma unroll
-    for (int k = 0; k < 4; k++)
-    {
-        const float2 h = half2_bits_to_float2(words[k]);
-        const float d = k < 2 ? d_lo : d_hi;
-        // (g16 * inv) is the unscaled fp32 gradient of the reference, then * clip
-        adamw_element(pp.v[2 * k], mm.v[2 * k], vv.v[2 * k], (h.x * f.inv) * f.coef, f.w1, f.w2, f.b2, f.eps, d,
-                      f.step_size, f.bc2_sqrt);
-        adamw_element(pp.v[2 * k + 1], mm.v[2 * k + 1], vv.v[2 * k + 1], (h.y * f.inv) * f.coef, f.w1, f.w2, f.b2,
-                      f.eps, d, f.step_size, f.bc2_sqrt);
-    }
-    store8<ST>(master + e, pp);
-    store8<ST>(m + e, mm);
-    store8<ST>(v + e, vv);
-    if (w16 != nullptr)
-    {
-        uint4 out;
-        out.x = float2_to_half2_bits(pp.v[0], pp.v[1]);
-        out.y = float2_to_half2_bits(pp.v[2], pp.v[3]);
-        out.z = float2_to_half2_bits(pp.v[4], pp.v[5]);
-        out.w = float2_to_half2_bits(pp.v[6], pp.v[7]);
-        store_h8<ST>(w16 + j, out);
-    }
-}
-
 // The whole grid sweeps the arena together: group i of a sweep belongs to thread i mod
 // (grid * THREADS). A thread's positions only grow, so it walks the tensor table once; while
 // its groups stay inside one tensor the decay lookup is a single compare (group_decay).
@@ -96,7 +51,7 @@ __global__ void __launch_bounds__(THREADS)
         return;                                 // skipped step: nothing moves
     }
     const float wd_decay = st->decay;
-    const StepFactors f = {st->clip_coef, st->step_size, st->bc2_sqrt, st->inv_scale, 1.0f - b1, 1.0f - b2, b2, eps};
+    const StepFactors f = step_factors(st, b1, b2, eps);
 
     // group indices fit 32 bits (the launcher refuses ranges beyond 2^31 - 2^23 groups): one
     // multiply-add makes each address, and the loop counter is a single register
@@ -112,8 +67,15 @@ __global__ void __launch_bounds__(THREADS)
     {
         const long long at = arena_offset + static_cast<long long>(i) * 8;
         update_group<ST>(
-            master, m, v, g16, w16, i,
-            [&](float &d_lo, float &d_hi) { group_decay(cur, tab, nruns, at, wd_decay, d_lo, d_hi); }, f);
+            master, m, v, g16, i,
+            [&](float &d_lo, float &d_hi) { group_decay(cur, tab, nruns, at, wd_decay, d_lo, d_hi); },
+            [&](int j, const uint4 &half8) {
+                if (w16 != nullptr)
+                {
+                    store_h8<ST>(w16 + j, half8);
+                }
+            },
+            f);
     }
 }
 

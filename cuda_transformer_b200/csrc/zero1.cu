@@ -184,53 +184,32 @@ __global__ void __launch_bounds__(256)
     {
         return;                                 // skipped step: no rank's arena is touched
     }
-    const float coef = st->clip_coef;
-    const float step_size = st->step_size;
-    const float bc2_sqrt = st->bc2_sqrt;
     const float wd_decay = st->decay;
-    const float inv = st->inv_scale;
-    const float w1 = 1.0f - b1;
-    const float w2 = 1.0f - b2;
+    const StepFactors f = step_factors(st, b1, b2, eps);
 
-    const long long stride = static_cast<long long>(gridDim.x) * THREADS;
-    long long i = static_cast<long long>(blockIdx.x) * THREADS + threadIdx.x;
-    if (i >= n8)
+    // 32-bit group indices, as pass2_f16_kernel (the launcher refuses longer ranges)
+    const int groups = static_cast<int>(n8);
+    const int stride = static_cast<int>(gridDim.x) * THREADS;
+    int i = static_cast<int>(blockIdx.x) * THREADS + static_cast<int>(threadIdx.x);
+    if (i >= groups)
     {
         return;
     }
-    Cursor cur = cursor_seek(tab, nruns, arena_offset + i * 8, wd_decay);
-    for (; i < n8; i += stride)
+    Cursor cur = cursor_seek(tab, nruns, arena_offset + static_cast<long long>(i) * 8, wd_decay);
+    for (; i < groups; i += stride)
     {
-        const uint4 gw = load_h8<0>(g16 + i);
-        Float8 pp = load8<0>(master + i * 8);
-        Float8 mm = load8<0>(m + i * 8);
-        Float8 vv = load8<0>(v + i * 8);
-        float d_lo, d_hi;
-        group_decay(cur, tab, nruns, arena_offset + i * 8, wd_decay, d_lo, d_hi);
-        const uint32_t words[4] = {gw.x, gw.y, gw.z, gw.w};
+        const long long at = arena_offset + static_cast<long long>(i) * 8;
+        update_group<1>(
+            master, m, v, g16, i,
+            [&](float &d_lo, float &d_hi) { group_decay(cur, tab, nruns, at, wd_decay, d_lo, d_hi); },
+            [&](int j, const uint4 &half8) {
 #pragma unroll
-        for (int k = 0; k < 4; k++)
-        {
-            const float2 f = half2_bits_to_float2(words[k]);
-            const float d = k < 2 ? d_lo : d_hi;
-            adamw_element(pp.v[2 * k], mm.v[2 * k], vv.v[2 * k], (f.x * inv) * coef, w1, w2, b2, eps, d, step_size,
-                          bc2_sqrt);
-            adamw_element(pp.v[2 * k + 1], mm.v[2 * k + 1], vv.v[2 * k + 1], (f.y * inv) * coef, w1, w2, b2, eps, d,
-                          step_size, bc2_sqrt);
-        }
-        store8<1>(master + i * 8, pp);
-        store8<1>(m + i * 8, mm);
-        store8<1>(v + i * 8, vv);
-        uint4 out;
-        out.x = float2_to_half2_bits(pp.v[0], pp.v[1]);
-        out.y = float2_to_half2_bits(pp.v[2], pp.v[3]);
-        out.z = float2_to_half2_bits(pp.v[4], pp.v[5]);
-        out.w = float2_to_half2_bits(pp.v[6], pp.v[7]);
-#pragma unroll
-        for (int r = 0; r < R; r++)
-        {
-            store_h8<B200AMP_AG_STORE_HINT>(static_cast<uint4 *>(dst.p[r]) + i, out);
-        }
+                for (int r = 0; r < R; r++)
+                {
+                    store_h8<B200AMP_AG_STORE_HINT>(static_cast<uint4 *>(dst.p[r]) + j, half8);
+                }
+            },
+            f);
     }
 }
 
@@ -312,6 +291,11 @@ extern "C" B200AMP_API int b200amp_pass2_ag_f16(float *master, float *m, float *
                         weights16_by_rank != nullptr,
                     "pass2_ag: null pointer");
     B200AMP_REQUIRE(n > 0 && n % 8 == 0, "pass2_ag: n = %lld must be a positive multiple of 8", n);
+    if (n / 8 > (1LL << 31) - (1LL << 23))      // 32-bit group indices; the largest grid strides by < 2^23 groups
+    {
+        set_error("pass2_ag: n = %lld is beyond the 17,112,760,320 elements one launch addresses; split the range", n);
+        return B200AMP_ERR_LIMIT;
+    }
     B200AMP_REQUIRE(arena_offset >= 0 && arena_offset % 4 == 0, "pass2_ag: arena_offset = %lld must be a multiple "
                                                                  "of 4", arena_offset);
     B200AMP_REQUIRE(aligned(master, 32) && aligned(m, 32) && aligned(v, 32),

@@ -132,6 +132,16 @@ def test_fused_entry_points_reject_bad_arguments():
     with pytest.raises(amp.B200AmpError):
         amp.pass2_ag_f16(g.master, g.m, g.v, red, [g.weights16.data_ptr() + 2], 64, 0, g.tensors, 1, g.state,
                          0.9, 0.95, 1e-8)
+    # ranges longer than one launch addresses with 32-bit group indices are refused before anything runs
+    from cuda_transformer_b200 import _lib
+    too_long = 8 * ((1 << 31) - (1 << 23) + 1)
+    for call in (lambda: amp.pass2_ag_f16(g.master, g.m, g.v, red, [g.weights16.data_ptr()], too_long, 0, g.tensors,
+                                          1, g.state, 0.9, 0.95, 1e-8),
+                 lambda: amp.pass2_f16(g.master, g.m, g.v, red, g.weights16, too_long, 0, g.tensors, 1, g.state,
+                                       0.9, 0.95, 1e-8)):
+        with pytest.raises(amp.B200AmpError, match="beyond") as err:
+            call()
+        assert err.value.status == _lib.ERR_LIMIT
 
 
 # ---------------------------------------------------------------- two real GPUs
