@@ -39,9 +39,14 @@ int sm_count()
     static std::atomic<int> cache[MAX_DEVICES];
     int dev = -1;
     cudaError_t err = cudaGetDevice(&dev);
-    if (err != cudaSuccess || dev < 0 || dev >= MAX_DEVICES)
+    if (err != cudaSuccess)
     {
         cuda_fail(err, "cudaGetDevice", __FILE__, __LINE__);
+        return -1;
+    }
+    if (dev < 0 || dev >= MAX_DEVICES)
+    {
+        set_error("device index %d is outside the %d devices this library keeps state for", dev, MAX_DEVICES);
         return -1;
     }
     int have = cache[dev].load(std::memory_order_relaxed);

@@ -15,6 +15,7 @@
 
 #include <climits>
 #include <cmath>
+#include <mutex>
 
 #include "pass1_common.cuh"
 
@@ -475,8 +476,6 @@ extern "C" B200AMP_API int b200amp_finalize_sums(b200amp_step_state *st, const d
 // acceptable. The scratch that pass 1 needs (one fp64 partial per virtual block, the ticket, the
 // flag word) lives in the library image instead: every GPU that loads the library holds these
 // 37,920 bytes until the process exits.
-
-#include <mutex>
 
 namespace b200amp
 {
