@@ -372,6 +372,31 @@ def run_gpu(args) -> dict:
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
 
+    skipped_step = None
+    if world == 1:
+        # A skipped step (an inf among the gradients) moves 2 B/param: pass 1 reads the arena, pass 2
+        # returns at once. Timed apart from the metric; state and gradients are put back afterwards.
+        saved_state, saved_head = opt.state.clone(), opt.grads16[:8].clone()
+        opt.grads16[0] = float("inf")
+        reps = 5
+        step_fn()
+        s0 = torch.cuda.Event(enable_timing=True)
+        s1 = torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        s0.record()
+        for _ in range(reps):
+            step_fn()
+        s1.record()
+        torch.cuda.synchronize()
+        if opt.read_state().skipped != reps + 1:
+            raise SystemExit("the steps with an inf gradient were not skipped")
+        skip_ms = s0.elapsed_time(s1) / reps
+        skipped_step = {"ms_per_step": skip_ms, "hbm_gbs": BYTES_PASS1 * n / (skip_ms * 1e-3) / 1e9,
+                        "bytes_per_param": BYTES_PASS1, "steps": reps}
+        opt.state.copy_(saved_state)
+        opt.grads16[:8].copy_(saved_head)
+        torch.cuda.synchronize()
+
     if world > 1:
         dist.barrier()
 
@@ -405,6 +430,8 @@ def run_gpu(args) -> dict:
     }
     if phases:
         line["phases"] = phases
+    if skipped_step:
+        line["skipped_step"] = skipped_step
     line["roofline"]["traffic"] = PASS2_DRAM_BYTES_PER_PARAM_NCU * n_local
     line["roofline"]["traffic_source"] = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on the "
                                           "gpt2-small arena (profiles/), scaled by the element count")
