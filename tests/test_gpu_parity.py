@@ -738,3 +738,81 @@ def test_compat_adamw_wide_and_narrow_forms_agree(G, O):
     for a, b in zip(wide.host(), full.host()):
         assert np.array_equal(a[4:], b[4:])
     assert np.array_equal(full.host()[0][:4], init[:4])         # the first quad was outside the narrow call
+
+
+def test_growth_after_2000_clean_steps_as_the_reference_run(G, O):
+    """The reference's production setting (growth_interval 2000, cuda/gpt_fast.cu:142-143; its
+    training log shows S going 65,536 -> 131,072 at step 2000): 2001 graph replays of the step on
+    a small arena against the oracle, with the whole history ring compared at the end."""
+    from cuda_transformer_b200 import amp
+    n = 8 * 512
+    rng = np.random.default_rng(2000)
+    init = (rng.standard_normal(n) * 0.02).astype(np.float32)
+    bits = (rng.standard_normal(n) * 1e-3 * 65536.0).astype(np.float16).view(np.uint16)
+    table = [(0, n // 4, 0), (n // 4, n - n // 4, 1)]
+    cfg = amp.make_schedule(lr=6e-4, min_lr=6e-5, warmup_steps=100, max_steps=2500, growth_interval=2000)
+    ocfg = O.make_schedule(lr=6e-4, min_lr=6e-5, warmup_steps=100, max_steps=2500, growth_interval=2000)
+    g = G.GpuStep(init, table, cfg, loss_scale=65536.0, history_len=4096)
+    g.set_grads16(bits)
+    ora = O.OracleStep(init, table, ocfg, loss_scale=65536.0, history_len=4096)
+    stream = torch.cuda.Stream()
+    graph = amp.CudaGraph()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(stream):
+        graph.capture(stream, lambda: g.step_f16())
+    for _ in range(2001):
+        graph.launch(stream)
+    stream.synchronize()
+    for _ in range(2001):
+        ora.step_f16(bits)          # the same scaled gradients every step: step 2000 sees them at S = 131072
+    st = g.read_state()
+    assert st.step == 2001 and st.adam_t == 2001 and st.skipped == 0
+    assert st.loss_scale == 131072.0 and st.good_steps == 1
+    G.assert_states_equal(st, ora.state, tol=1e-6)
+    hist = np.frombuffer(g.history.cpu().numpy().tobytes(), dtype=np.float32).reshape(4096, 15)
+    scales = hist[:2001, 0]
+    assert np.all(scales[:1999] == 65536.0) and scales[1999] == 131072.0 and scales[2000] == 131072.0
+    lrs = hist[:2001, 7].astype(np.float64)
+    want = np.array([O.lr_at(k, ocfg) for k in range(2001)])
+    assert np.max(np.abs(lrs - want) / want) <= 1e-6
+    gm, gmm, gv, gw = g.host()
+    for got, ref in ((gm, ora.master), (gmm, ora.m), (gv, ora.v)):
+        assert H.rel_err(ref, got) <= 2e-6, "2001 steps of one-ulp differences may add up to a little over 1e-6"
+    assert H.half_ulp_distance(ora.weights16, gw) <= 1
+
+
+def test_zero_rows_with_zero_gradient_stay_zero(G):
+    """The optimizer half of padded_rows (reference/test_reference.py:113-116) on the GPU, native
+    and compat path: zero parameter + zero gradient stays +0.0 exactly under weight decay, and so
+    does the arena's alignment padding in AmpOptimizer."""
+    from cuda_transformer_b200 import amp
+    n = 8 * 256
+    rng = np.random.default_rng(4)
+    init = (rng.standard_normal(n) * 0.02).astype(np.float32)
+    pad = slice(8 * 100, 8 * 140)
+    init[pad] = 0.0
+    table = [(0, 8 * 200, 1), (8 * 200, n - 8 * 200, 0)]
+    native = G.GpuStep(init, table, sched(amp), loss_scale=65536.0)
+    compat = G.GpuStep(init, table, sched(amp), loss_scale=65536.0)
+    for k in range(5):
+        g = (rng.standard_normal(n) * 1e-3 * 65536.0).astype(np.float16)
+        g[pad] = 0.0
+        native.set_grads16(g.view(np.uint16))
+        native.step_f16()
+        compat.step_f32(g.astype(np.float32))
+    for step in (native, compat):
+        master, m, v, w16 = step.host()
+        for arr in (master, m, v):
+            assert np.all(arr[pad].view(np.uint32) == 0), "a padded row moved (or turned into -0.0)"
+        assert np.all(w16[pad] == 0)
+        assert np.all(master[:8 * 100] != init[:8 * 100])
+    slots = H.debug_slots()
+    opt = amp.AmpOptimizer(slots, sched(amp), loss_scale=65536.0)
+    opt.set_params(torch.from_numpy(H.debug_init()))
+    assert opt.n > opt.n_params or opt.n % 1024 == 0
+    opt.grads16[: opt.n_params].copy_((torch.randn(opt.n_params) * 1e-3 * 65536.0).half())
+    for _ in range(3):
+        opt.optimizer_step()
+    tail = slice(opt.n_params, opt.n)
+    for t in (opt.master, opt.m, opt.v, opt.weights16):
+        assert not torch.any(t[tail] != 0)

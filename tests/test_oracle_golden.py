@@ -186,3 +186,24 @@ def test_amp_path_100_steps_trajectory_and_state(contract):
     for what, arr in (("p", step.master), ("m", step.m), ("v", step.v)):
         assert H.rel_err(gold[what], arr[::stride]) <= H.STATE_TOL, what
     assert H.half_ulp_distance(gold["w16"], step.weights16[::stride]) <= 1
+
+
+def test_zero_rows_with_zero_gradient_stay_zero():
+    """The optimizer half of padded_rows (reference/test_reference.py:113-116): vocabulary padding
+    rows start at 0, get no gradient, and an optimizer step with weight decay must leave them at
+    +0.0 exactly (and their m, v, fp16 copy too)."""
+    n = 8 * 256
+    rng = np.random.default_rng(4)
+    init = (rng.standard_normal(n) * 0.02).astype(np.float32)
+    pad = slice(8 * 100, 8 * 140)                       # rows of a decayed 2-D tensor that are padding
+    init[pad] = 0.0
+    table = [(0, 8 * 200, 1), (8 * 200, n - 8 * 200, 0)]
+    ora = O.OracleStep(init, table, O.make_schedule(), loss_scale=65536.0)
+    for k in range(5):
+        g = (rng.standard_normal(n) * 1e-3 * ora.state.loss_scale).astype(np.float16)
+        g[pad] = 0.0
+        ora.step_f16(g.view(np.uint16))
+    for arr in (ora.master, ora.m, ora.v):
+        assert np.all(arr[pad].view(np.uint32) == 0), "a padded row moved (or turned into -0.0)"
+    assert np.all(ora.weights16[pad] == 0)
+    assert np.all(ora.master[:8 * 100] != init[:8 * 100])      # the rest did move
