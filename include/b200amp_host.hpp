@@ -101,6 +101,7 @@ struct DeviceArray                      // one cudaMalloc, freed in the destruct
 struct AmpOptimizer
 {
     long long n = 0;                    // elements in the arena, a multiple of 8
+    int device = 0;                     // the device that was current at construction; methods switch to it
     cudaStream_t stream = nullptr;
     DeviceArray<float> master, m, v;
     DeviceArray<__half> weights16, grads16;
@@ -117,6 +118,7 @@ struct AmpOptimizer
           history(history_len_), workspace(b200amp_workspace_bytes()), history_len(history_len_), sched(cfg),
           beta1(cfg.beta1), beta2(cfg.beta2), eps(eps_)
     {
+        B200AMP_HOST_CUDA(cudaGetDevice(&device));
         B200AMP_HOST_CHECK(b200amp_device_check());
         B200AMP_HOST_CUDA(cudaStreamCreate(&stream));       // blocking, as cuda/gpt_fast.cu:94
         B200AMP_HOST_CUDA(cudaMemcpy(tensors.ptr, table.data(), table.size() * sizeof(b200amp_tensor_info),
@@ -137,6 +139,7 @@ struct AmpOptimizer
 
     void reset(float loss_scale)                            // cuda/gpt_fast.cu:245-253
     {
+        B200AMP_HOST_CUDA(cudaSetDevice(device));
         m.zero(stream);
         v.zero(stream);
         grads16.zero(stream);
@@ -154,18 +157,21 @@ struct AmpOptimizer
             fprintf(stderr, "error: %zu parameters given, the arena has %lld\n", host.size(), n);
             exit(1);
         }
+        B200AMP_HOST_CUDA(cudaSetDevice(device));
         B200AMP_HOST_CUDA(cudaMemcpy(master.ptr, host.data(), host.size() * sizeof(float), cudaMemcpyHostToDevice));
         B200AMP_HOST_CHECK(b200amp_cast_to_x(weights16.ptr, master.ptr, n, stream));
         B200AMP_HOST_CUDA(cudaStreamSynchronize(stream));
     }
     void set_grads(const std::vector<__half> &host)         // what the backward pass would leave
     {
+        B200AMP_HOST_CUDA(cudaSetDevice(device));
         B200AMP_HOST_CUDA(cudaMemcpyAsync(grads16.ptr, host.data(), host.size() * sizeof(__half),
                                           cudaMemcpyHostToDevice, stream));
         B200AMP_HOST_CUDA(cudaStreamSynchronize(stream));
     }
     void optimizer_step()                                   // the place of cuda/gpt_fast.cu:438-450
     {
+        B200AMP_HOST_CUDA(cudaSetDevice(device));
         B200AMP_HOST_CHECK(b200amp_step_f16(master.ptr, m.ptr, v.ptr, grads16.ptr, weights16.ptr, n, tensors.ptr,
                                             static_cast<int>(tensors.count), state.ptr, workspace.ptr, &sched,
                                             history.ptr, history_len, beta1, beta2, eps, stream));
@@ -173,6 +179,7 @@ struct AmpOptimizer
     b200amp_step_state read_state()                         // cuda/gpt_fast.cu:461-467
     {
         b200amp_step_state st;
+        B200AMP_HOST_CUDA(cudaSetDevice(device));
         B200AMP_HOST_CUDA(cudaMemcpyAsync(&st, state.ptr, sizeof(st), cudaMemcpyDeviceToHost, stream));
         B200AMP_HOST_CUDA(cudaStreamSynchronize(stream));
         return st;

@@ -1,5 +1,6 @@
-"""Builds tests/cpp/bin/test_amp_host from test_amp_host.cpp (host-only C++ over the C ABI),
-linked against the in-tree libb200amp.so with an rpath relative to the binary."""
+"""Builds the C++ test programs of the host layers (host-only C++ over the C ABI) into
+tests/cpp/bin/, linked against the in-tree libb200amp.so with an rpath relative to the binary:
+test_amp_host (one GPU: shim + AmpOptimizer) and test_zero1_host (one process, R ranks)."""
 from __future__ import annotations
 
 import os
@@ -8,27 +9,36 @@ import subprocess
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REPO = os.path.dirname(os.path.dirname(HERE))
-SRC = os.path.join(HERE, "test_amp_host.cpp")
 BIN_DIR = os.path.join(HERE, "bin")
-BIN = os.path.join(BIN_DIR, "test_amp_host")
 LIB_DIR = os.path.join(REPO, "cuda_transformer_b200", "lib")
+INCLUDE = os.path.join(REPO, "include")
+PROGRAMS = {
+    "test_amp_host": ["b200amp.h", "b200amp_host.hpp", os.path.join("compat", "fast_shim.h")],
+    "test_zero1_host": ["b200amp.h", "b200amp_host.hpp", "b200amp_zero1_host.hpp"],
+}
+BIN = os.path.join(BIN_DIR, "test_amp_host")
 
 
-def build(force: bool = False) -> str:
-    deps = [SRC, os.path.join(REPO, "include", "b200amp.h"), os.path.join(REPO, "include", "b200amp_host.hpp"),
-            os.path.join(REPO, "include", "compat", "fast_shim.h")]
-    if not force and os.path.exists(BIN) and all(os.path.getmtime(BIN) >= os.path.getmtime(d) for d in deps):
-        return BIN
+def build(force: bool = False, program: str = "test_amp_host") -> str:
+    src = os.path.join(HERE, program + ".cpp")
+    exe = os.path.join(BIN_DIR, program)
+    deps = [src] + [os.path.join(INCLUDE, h) for h in PROGRAMS[program]]
+    if not force and os.path.exists(exe) and all(os.path.getmtime(exe) >= os.path.getmtime(d) for d in deps):
+        return exe
     os.makedirs(BIN_DIR, exist_ok=True)
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     cmd = [nvcc, "-O2", "-std=c++17", "-x", "cu", "-gencode", "arch=compute_100a,code=sm_100a",
-           "-I", os.path.join(REPO, "include"), SRC, "-o", BIN,
+           "-I", INCLUDE, src, "-o", exe,
            "-L", LIB_DIR, "-lb200amp", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../../cuda_transformer_b200/lib"]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
-        raise RuntimeError("building test_amp_host failed:\n" + " ".join(cmd) + "\n" + proc.stderr)
-    return BIN
+        raise RuntimeError(f"building {program} failed:\n" + " ".join(cmd) + "\n" + proc.stderr)
+    return exe
+
+
+def build_all(force: bool = False) -> list:
+    return [build(force, program) for program in PROGRAMS]
 
 
 if __name__ == "__main__":
-    print(build(force=True))
+    print(build_all(force=True))

@@ -15,8 +15,9 @@ def test_cpp_host_program_builds():
     import build_host_test
     from cuda_transformer_b200 import build as lib_build
     lib_build.build()
-    exe = build_host_test.build()
-    assert os.path.exists(exe) and exe.endswith("test_amp_host")
+    exes = build_host_test.build_all()
+    assert [os.path.basename(e) for e in exes] == ["test_amp_host", "test_zero1_host"]
+    assert all(os.path.exists(e) for e in exes)
 
 
 @pytest.mark.gpu
@@ -28,3 +29,17 @@ def test_cpp_host_program_checks_pass():
     sys.stderr.write(proc.stderr)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-2000:]
     assert "all checks passed" in proc.stdout and "FAILED" not in proc.stdout
+
+
+@pytest.mark.gpu
+def test_cpp_zero1_host_program_checks_pass():
+    """One process, R = 1, 2, 4, 8 ranks over the GPUs present (all on one GPU where there is one),
+    events between the phases, against the one-GPU step on the averaged gradients."""
+    import build_host_test
+    exe = build_host_test.build(program="test_zero1_host")
+    proc = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    sys.stdout.write(proc.stdout)
+    sys.stderr.write(proc.stderr)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-2000:]
+    assert "all checks passed" in proc.stdout and "FAILED" not in proc.stdout
+    assert proc.stdout.count(" ok\n") == 4 * 10
