@@ -34,7 +34,8 @@ __all__ = [
     "StepState", "ScheduleConfig", "TensorInfo", "B200AmpError",
     "initial_state", "begin_step", "unscale_and_norm", "finalize_step", "adamw_multi", "lr_on_gpu",
     "cast_to_x", "CudaGraph", "AmpOptimizer", "Zero1Step", "ShardedAmpOptimizer", "make_schedule",
-    "pass1_f16", "pass1_f16_static", "cast_pass1_f32", "pass1_finalize_f16", "rs_pass1_f16", "pass2_ag_f16", "FusedZero1Optimizer", "finalize_sums", "pass2_f16", "step_f16",
+    "pass1_f16", "pass1_f16_static", "cast_pass1_f32", "pass1_finalize_f16", "rs_pass1_f16", "pass2_ag_f16",
+    "FusedZero1Optimizer", "finalize_sums", "pass2_f16", "step_f16",
 ]
 
 
