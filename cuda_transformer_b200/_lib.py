@@ -59,6 +59,7 @@ PROTOTYPES = {
     "b200amp_last_error": (C.c_char_p, []),
     "b200amp_version": (C.c_char_p, []),
     "b200amp_device_check": (_I, []),
+    "b200amp_check_tensor_table": (_I, [_P, _I, _LL]),
     "b200amp_initial_state": (_I, [_F, C.POINTER(StepState)]),
     "b200amp_begin_step": (_I, [_P, _P]),
     "b200amp_unscale_and_norm_f32": (_I, [_P, _LL, _P, _P, _P]),

@@ -35,7 +35,7 @@ __all__ = [
     "initial_state", "begin_step", "unscale_and_norm", "finalize_step", "adamw_multi", "lr_on_gpu",
     "cast_to_x", "CudaGraph", "AmpOptimizer", "Zero1Step", "ShardedAmpOptimizer", "make_schedule",
     "pass1_f16", "pass1_f16_static", "cast_pass1_f32", "pass1_finalize_f16", "rs_pass1_f16", "pass2_ag_f16",
-    "FusedZero1Optimizer", "finalize_sums", "pass2_f16", "step_f16",
+    "FusedZero1Optimizer", "finalize_sums", "pass2_f16", "step_f16", "check_tensor_table",
 ]
 
 
@@ -230,7 +230,15 @@ def _upload_struct(struct_obj, device) -> torch.Tensor:
     return host.to(device)
 
 
-def _tensor_table_device(table: Sequence[Tuple[int, int, int]], device) -> torch.Tensor:
+def check_tensor_table(table: Sequence[Tuple[int, int, int]], n: int = 0) -> None:
+    """Raises B200AmpError unless the (offset, count, decay) rows are a table the kernels can
+    trust: ascending, offsets multiples of 4, no overlap, inside n elements when n > 0."""
+    arr = (TensorInfo * max(1, len(table)))(*[TensorInfo(o, c, d) for o, c, d in table])
+    check(_lib.load().b200amp_check_tensor_table(C.cast(arr, C.c_void_p), len(table), n))
+
+
+def _tensor_table_device(table: Sequence[Tuple[int, int, int]], device, n: int = 0) -> torch.Tensor:
+    check_tensor_table(table, n)
     arr = (TensorInfo * len(table))(*[TensorInfo(o, c, d) for o, c, d in table])
     host = torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8)
     return host.to(device)
@@ -261,7 +269,7 @@ class AmpOptimizer:
             table.append((self.n_params, self.n - self.n_params, 0))       # zero padding: never decayed
         self.ntensors = len(table)
         with torch.cuda.device(self.device):
-            self.tensors = _tensor_table_device(table, self.device)
+            self.tensors = _tensor_table_device(table, self.device, self.n)
             self.master = torch.zeros(self.n, dtype=torch.float32, device=self.device)
             self.m = torch.zeros_like(self.master)
             self.v = torch.zeros_like(self.master)
@@ -458,7 +466,7 @@ class ShardedAmpOptimizer(Zero1Step):
         with torch.cuda.device(device):
             check(self.lib.b200amp_device_check())
             super().__init__(slots, cfg, eps, loss_scale, history_len, device, group)
-            self.tensors = _tensor_table_device(self.table, self.device)
+            self.tensors = _tensor_table_device(self.table, self.device, self.n)
             self.workspace = torch.zeros(self.lib.b200amp_workspace_bytes(), dtype=torch.uint8, device=self.device)
             # pass 1 publishes {sum, flag} in the first 16 bytes of its workspace
             self.sums_local = self.workspace[:16].view(torch.float64)

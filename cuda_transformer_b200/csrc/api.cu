@@ -123,6 +123,34 @@ extern "C" B200AMP_API int b200amp_device_check(void)
     return B200AMP_OK;
 }
 
+extern "C" B200AMP_API int b200amp_check_tensor_table(const b200amp_tensor_info *host_table, int ntensors,
+                                                      long long n)
+{
+    B200AMP_REQUIRE(host_table != nullptr, "tensor table: null pointer");
+    B200AMP_REQUIRE(ntensors > 0 && ntensors <= B200AMP_MAX_TENSORS, "tensor table: %d entries, must be 1..%d",
+                    ntensors, B200AMP_MAX_TENSORS);
+    for (int k = 0; k < ntensors; k++)
+    {
+        const b200amp_tensor_info &t = host_table[k];
+        B200AMP_REQUIRE(t.offset >= 0 && t.offset % 4 == 0, "tensor table: entry %d starts at %lld, not a multiple "
+                                                            "of 4", k, t.offset);
+        B200AMP_REQUIRE(t.count > 0, "tensor table: entry %d has %lld elements", k, t.count);
+        B200AMP_REQUIRE(t.decay == 0 || t.decay == 1, "tensor table: entry %d has decay flag %d", k, t.decay);
+        if (k + 1 < ntensors)
+        {
+            B200AMP_REQUIRE(t.offset + t.count <= host_table[k + 1].offset,
+                            "tensor table: entry %d (%lld + %lld) reaches into entry %d (%lld)", k, t.offset, t.count,
+                            k + 1, host_table[k + 1].offset);
+        }
+        else if (n > 0)
+        {
+            B200AMP_REQUIRE(t.offset + t.count <= n, "tensor table: entry %d ends at %lld, the arena has %lld "
+                                                     "elements", k, t.offset + t.count, n);
+        }
+    }
+    return B200AMP_OK;
+}
+
 extern "C" B200AMP_API int b200amp_tune_set(const char *key, int value)
 {
     B200AMP_REQUIRE(key != nullptr, "tune_set: key is null");

@@ -106,6 +106,14 @@ typedef struct b200amp_tensor_info
     int decay;              /* 1: weight decay applies (>= 2-D weights), 0: it does not */
 } b200amp_tensor_info;
 
+/* Set-up check of a HOST copy of the tensor table (the kernels read the device copy and, like the
+ * reference's, trust it): 1..B200AMP_MAX_TENSORS entries, offsets multiples of 4 and ascending,
+ * counts positive, no entry reaching into the next, and, when n > 0, none past the n elements of
+ * the arena. The reference builds its table in code (cuda/gpt_fast.cu:105-115) and checks nothing;
+ * a table that arrives from a file or another program should go through this once. Host only:
+ * no CUDA call. */
+B200AMP_API int b200amp_check_tensor_table(const b200amp_tensor_info *host_table, int ntensors, long long n);
+
 #define B200AMP_NORM_BLOCKS 512     /* partial[] length of the compat path (cuda/kernels/fast.h:150) */
 #define B200AMP_MAX_TENSORS 1024    /* longest tensor table (cuda/kernels/fast.h:163) */
 

@@ -120,6 +120,7 @@ struct AmpOptimizer
     {
         B200AMP_HOST_CUDA(cudaGetDevice(&device));
         B200AMP_HOST_CHECK(b200amp_device_check());
+        B200AMP_HOST_CHECK(b200amp_check_tensor_table(table.data(), static_cast<int>(table.size()), n));
         B200AMP_HOST_CUDA(cudaStreamCreate(&stream));       // blocking, as cuda/gpt_fast.cu:94
         B200AMP_HOST_CUDA(cudaMemcpy(tensors.ptr, table.data(), table.size() * sizeof(b200amp_tensor_info),
                                      cudaMemcpyHostToDevice));

@@ -84,6 +84,7 @@ struct Zero1Group
             fprintf(stderr, "error: %lld elements do not split into %d slices of whole 8-element groups\n", n, nranks);
             exit(1);
         }
+        B200AMP_HOST_CHECK(b200amp_check_tensor_table(table.data(), static_cast<int>(table.size()), n));
         for (int a : devices)
         {
             B200AMP_HOST_CUDA(cudaSetDevice(a));

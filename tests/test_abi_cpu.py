@@ -102,3 +102,37 @@ def test_shard_ranges_tile_the_arena():
             assert b == at and (e - b) % 128 == 0
             at = e
         assert at == n
+
+
+def test_tensor_table_check_is_host_only_and_strict(lib):
+    """b200amp_check_tensor_table: what the kernels assume about the table, checked once on the host."""
+    from cuda_transformer_b200 import amp
+
+    def status(rows, n=0):
+        arr = (_lib.TensorInfo * max(1, len(rows)))(*[_lib.TensorInfo(o, c, d) for o, c, d in rows])
+        return lib.b200amp_check_tensor_table(C.cast(arr, C.c_void_p), len(rows), n), lib.b200amp_last_error().decode()
+
+    for name, cfg in CONFIGS.items():
+        slots = param_layout(cfg)
+        assert status(list(tensor_table(slots)), padded(num_params(slots)))[0] == _lib.OK, name
+    assert status([(0, 8, 1), (8, 4, 0), (12, 4, 1)], 16)[0] == _lib.OK
+    assert status([(0, 8, 1), (12, 4, 0)], 16)[0] == _lib.OK                  # a hole between tensors is allowed
+    bad = {
+        "no entries": ([], 0),
+        "offset 6": ([(6, 8, 1)], 0),
+        "negative offset": ([(-4, 8, 1)], 0),
+        "empty tensor": ([(0, 0, 1)], 0),
+        "overlap": ([(0, 12, 1), (8, 4, 0)], 0),
+        "descending": ([(8, 4, 1), (0, 4, 0)], 0),
+        "past the arena": ([(0, 8, 1), (8, 12, 0)], 16),
+        "decay flag 2": ([(0, 8, 2)], 0),
+    }
+    for name, (rows, n) in bad.items():
+        code, text = status(rows, n)
+        assert code == _lib.ERR_ARG and text.startswith("tensor table"), (name, code, text)
+    assert lib.b200amp_check_tensor_table(None, 1, 0) == _lib.ERR_ARG
+    too_many = [(4 * k, 4, k % 2) for k in range(1025)]
+    assert status(too_many)[0] == _lib.ERR_ARG
+    with pytest.raises(amp.B200AmpError, match="reaches into"):
+        amp.check_tensor_table([(0, 12, 1), (8, 4, 0)])
+    amp.check_tensor_table([(0, 8, 1), (8, 8, 0)], 16)
