@@ -1,6 +1,7 @@
 """Builds the C++ test programs of the host layers (host-only C++ over the C ABI) into
 tests/cpp/bin/, linked against the in-tree libb200amp.so with an rpath relative to the binary:
-test_amp_host (one GPU: shim + AmpOptimizer) and test_zero1_host (one process, R ranks)."""
+test_amp_host (one GPU: shim + AmpOptimizer), test_zero1_host (one process, R ranks) and the
+measurement program peer_bandwidth (two GPUs; plain CUDA, does not use the library)."""
 from __future__ import annotations
 
 import os
@@ -12,17 +13,19 @@ REPO = os.path.dirname(os.path.dirname(HERE))
 BIN_DIR = os.path.join(HERE, "bin")
 LIB_DIR = os.path.join(REPO, "cuda_transformer_b200", "lib")
 INCLUDE = os.path.join(REPO, "include")
-PROGRAMS = {
-    "test_amp_host": ["b200amp.h", "b200amp_host.hpp", os.path.join("compat", "fast_shim.h")],
-    "test_zero1_host": ["b200amp.h", "b200amp_host.hpp", "b200amp_zero1_host.hpp"],
+PROGRAMS = {     # name -> (source file, headers it depends on)
+    "test_amp_host": ("test_amp_host.cpp", ["b200amp.h", "b200amp_host.hpp", os.path.join("compat", "fast_shim.h")]),
+    "test_zero1_host": ("test_zero1_host.cpp", ["b200amp.h", "b200amp_host.hpp", "b200amp_zero1_host.hpp"]),
+    "peer_bandwidth": ("peer_bandwidth.cu", []),
 }
 BIN = os.path.join(BIN_DIR, "test_amp_host")
 
 
 def build(force: bool = False, program: str = "test_amp_host") -> str:
-    src = os.path.join(HERE, program + ".cpp")
+    source, headers = PROGRAMS[program]
+    src = os.path.join(HERE, source)
     exe = os.path.join(BIN_DIR, program)
-    deps = [src] + [os.path.join(INCLUDE, h) for h in PROGRAMS[program]]
+    deps = [src] + [os.path.join(INCLUDE, h) for h in headers]
     if not force and os.path.exists(exe) and all(os.path.getmtime(exe) >= os.path.getmtime(d) for d in deps):
         return exe
     os.makedirs(BIN_DIR, exist_ok=True)

@@ -1,0 +1,336 @@
+// peer_bandwidth.cu: what bounds a kernel that reads or writes another GPU's memory over NVLink.
+// A measurement program, not a test: it prints the bandwidth per direction of a 1 GiB copy between
+// GPU 0 and GPU 1 for each way of moving the bytes, first with one direction busy, then with both
+// GPUs copying against each other at once (the situation of the ZeRO-1 step, where every rank
+// pulls from and pushes to its peers at the same time):
+//
+//   copy engine    cudaMemcpyAsync
+//   SM ld / st     256-bit ld.global / st.global from a persistent grid (what rs_pass1 and
+//                  pass2_ag of the library issue)
+//   bulk           cp.async.bulk global -> shared -> global through a ring of stages, one thread
+//                  per CTA driving it (no multicast; every barrier wait bounded)
+//
+// One process, two devices, peer access on. Needs two GPUs; prints a note and exits 0 with fewer.
+// Built by tests/cpp/build_host_test.py.
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+
+#define CK(call)                                                                                     \
+    do                                                                                               \
+    {                                                                                                \
+        cudaError_t err_ = (call);                                                                   \
+        if (err_ != cudaSuccess)                                                                     \
+        {                                                                                            \
+            fprintf(stderr, "CUDA error at line %d: %s (%s)\n", __LINE__, cudaGetErrorString(err_), #call); \
+            exit(1);                                                                                 \
+        }                                                                                            \
+    } while (0)
+
+constexpr long long BYTES = 1LL << 30;
+constexpr int SM_GRID = 148 * 4;            // CTAs of the ld/st kernel
+constexpr int BULK_GRID = 148 * 2;
+constexpr int BULK_TILE = 16384;
+constexpr int BULK_STAGES = 6;
+constexpr unsigned WAIT_LIMIT = 1u << 20;   // polls of one barrier before the kernel gives up
+
+__device__ int g_gave_up = 0;
+
+// ---------------------------------------------------------------- SM loads and stores
+
+struct Float8
+{
+    float v[8];
+};
+
+__device__ __forceinline__ Float8 load8(const float *p)
+{
+    Float8 r;
+    asm volatile("ld.global.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=f"(r.v[0]), "=f"(r.v[1]), "=f"(r.v[2]), "=f"(r.v[3]), "=f"(r.v[4]), "=f"(r.v[5]), "=f"(r.v[6]),
+                   "=f"(r.v[7])
+                 : "l"(p));
+    return r;
+}
+
+__device__ __forceinline__ void store8(float *p, const Float8 &r)
+{
+    asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 :
+                 : "l"(p), "f"(r.v[0]), "f"(r.v[1]), "f"(r.v[2]), "f"(r.v[3]), "f"(r.v[4]), "f"(r.v[5]), "f"(r.v[6]),
+                   "f"(r.v[7])
+                 : "memory");
+}
+
+// two 32-byte groups per thread per trip, loads first
+__global__ void __launch_bounds__(256) sm_copy(const float *__restrict__ src, float *__restrict__ dst, long long n8)
+{
+    const long long stride = static_cast<long long>(gridDim.x) * 256;
+    long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+    for (; i + stride < n8; i += 2 * stride)
+    {
+        const Float8 a = load8(src + i * 8);
+        const Float8 b = load8(src + (i + stride) * 8);
+        store8(dst + i * 8, a);
+        store8(dst + (i + stride) * 8, b);
+    }
+    if (i < n8)
+    {
+        store8(dst + i * 8, load8(src + i * 8));
+    }
+}
+
+// ---------------------------------------------------------------- bulk copies through shared memory
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p)
+{
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ bool barrier_wait(uint64_t *bar, unsigned parity)
+{
+    for (unsigned tries = 0; tries < WAIT_LIMIT; tries++)
+    {
+        unsigned ok;
+        asm volatile("{\n\t.reg .pred p;\n\t"
+                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok)
+                     : "r"(smem_u32(bar)), "r"(parity)
+                     : "memory");
+        if (ok)
+        {
+            return true;
+        }
+        if (tries > 64)
+        {
+            __nanosleep(64);
+        }
+    }
+    return false;
+}
+
+__device__ __forceinline__ void request_tile(char *slot, const char *src, uint64_t *bar)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" : : "r"(smem_u32(bar)), "r"(BULK_TILE)
+                 : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :
+                 : "r"(smem_u32(slot)), "l"(src), "r"(BULK_TILE), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// Tile t of the buffer goes through slot (k mod stages) of CTA (t mod grid), k its index among the
+// CTA's tiles. The slot refilled at trip d was stored from at trip d - 2, so at most the newest
+// store group may still be reading shared memory when the refill is requested.
+__global__ void __launch_bounds__(32) bulk_copy(const char *__restrict__ src, char *__restrict__ dst, long long tiles)
+{
+    extern __shared__ __align__(128) char ring[];
+    __shared__ uint64_t full[BULK_STAGES];
+    if (threadIdx.x != 0)
+    {
+        return;                                 // one thread drives the whole pipeline
+    }
+    for (int s = 0; s < BULK_STAGES; s++)
+    {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" : : "r"(smem_u32(&full[s])) : "memory");
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" : : : "memory");
+    long long mine = 0;
+    for (long long t = blockIdx.x; t < tiles; t += gridDim.x)
+    {
+        mine++;
+    }
+    constexpr int AHEAD = BULK_STAGES - 2;
+    for (long long k = 0; k < AHEAD && k < mine; k++)
+    {
+        request_tile(ring + (k % BULK_STAGES) * BULK_TILE, src + (blockIdx.x + k * gridDim.x) * BULK_TILE,
+                     &full[k % BULK_STAGES]);
+    }
+    long long done = 0;
+    bool ok = true;
+    for (; done < mine; done++)
+    {
+        const long long next = done + AHEAD;
+        if (next < mine)
+        {
+            asm volatile("cp.async.bulk.wait_group.read 1;" : : : "memory");
+            request_tile(ring + (next % BULK_STAGES) * BULK_TILE, src + (blockIdx.x + next * gridDim.x) * BULK_TILE,
+                         &full[next % BULK_STAGES]);
+        }
+        if (!barrier_wait(&full[done % BULK_STAGES], static_cast<unsigned>((done / BULK_STAGES) & 1)))
+        {
+            ok = false;
+            break;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" : : : "memory");
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                     :
+                     : "l"(dst + (blockIdx.x + done * gridDim.x) * BULK_TILE),
+                       "r"(smem_u32(ring + (done % BULK_STAGES) * BULK_TILE)), "r"(BULK_TILE)
+                     : "memory");
+        asm volatile("cp.async.bulk.commit_group;" : : : "memory");
+    }
+    if (!ok)
+    {
+        g_gave_up = 1;
+        // loads already requested still target this CTA's shared memory: one more bounded wait each
+        const long long requested = done + AHEAD + 1 < mine ? done + AHEAD + 1 : mine;
+        for (long long k = done; k < requested; k++)
+        {
+            barrier_wait(&full[k % BULK_STAGES], static_cast<unsigned>((k / BULK_STAGES) & 1));
+        }
+    }
+    asm volatile("cp.async.bulk.wait_group 0;" : : : "memory");
+}
+
+// ---------------------------------------------------------------- host
+
+enum Mover
+{
+    COPY_ENGINE,
+    SM_LD_ST,
+    BULK
+};
+
+static const char *MOVER_NAMES[3] = {"copy engine", "SM ld / st (256-bit)", "bulk through shared memory"};
+
+static void enqueue(Mover how, const char *src, char *dst, cudaStream_t s)
+{
+    if (how == COPY_ENGINE)
+    {
+        CK(cudaMemcpyAsync(dst, src, BYTES, cudaMemcpyDefault, s));
+    }
+    else if (how == SM_LD_ST)
+    {
+        sm_copy<<<SM_GRID, 256, 0, s>>>(reinterpret_cast<const float *>(src), reinterpret_cast<float *>(dst), BYTES / 32);
+        CK(cudaGetLastError());
+    }
+    else
+    {
+        bulk_copy<<<BULK_GRID, 32, BULK_STAGES * BULK_TILE, s>>>(src, dst, BYTES / BULK_TILE);
+        CK(cudaGetLastError());
+    }
+}
+
+struct Side                                     // one GPU: a stream, two events, three buffers
+{
+    int device;
+    cudaStream_t stream;
+    cudaEvent_t begin, end;
+    char *a, *b;                                // local source and local destination
+};
+
+static Side make_side(int device, int peer)
+{
+    Side s;
+    s.device = device;
+    CK(cudaSetDevice(device));
+    CK(cudaDeviceEnablePeerAccess(peer, 0));
+    CK(cudaStreamCreate(&s.stream));
+    CK(cudaEventCreate(&s.begin));
+    CK(cudaEventCreate(&s.end));
+    CK(cudaMalloc(&s.a, BYTES));
+    CK(cudaMalloc(&s.b, BYTES));
+    CK(cudaMemset(s.a, device + 1, BYTES));
+    CK(cudaMemset(s.b, 0, BYTES));
+    CK(cudaFuncSetAttribute(bulk_copy, cudaFuncAttributeMaxDynamicSharedMemorySize, BULK_STAGES * BULK_TILE));
+    CK(cudaDeviceSynchronize());
+    return s;
+}
+
+static bool gave_up(const Side &s)
+{
+    int flag = 0;
+    CK(cudaSetDevice(s.device));
+    CK(cudaMemcpyFromSymbol(&flag, g_gave_up, sizeof(int)));
+    return flag != 0;
+}
+
+// read: each active side copies the OTHER side's `a` into its own `b`; write: its own `a` into the
+// other side's `b`. Returns GB/s per direction as seen by each side (0 for an idle side).
+static void run(Mover how, bool read, Side &x, Side &y, bool both, double out[2])
+{
+    Side *sides[2] = {&x, &y};
+    const int reps = 5;
+    for (int pass = 0; pass < 2; pass++)        // pass 0 warms up
+    {
+        for (int k = 0; k < (both ? 2 : 1); k++)
+        {
+            CK(cudaSetDevice(sides[k]->device));
+            CK(cudaEventRecord(sides[k]->begin, sides[k]->stream));
+        }
+        for (int i = 0; i < reps; i++)
+        {
+            for (int k = 0; k < (both ? 2 : 1); k++)
+            {
+                Side &me = *sides[k], &other = *sides[1 - k];
+                CK(cudaSetDevice(me.device));
+                enqueue(how, read ? other.a : me.a, read ? me.b : other.b, me.stream);
+            }
+        }
+        for (int k = 0; k < (both ? 2 : 1); k++)
+        {
+            CK(cudaSetDevice(sides[k]->device));
+            CK(cudaEventRecord(sides[k]->end, sides[k]->stream));
+        }
+        for (int k = 0; k < (both ? 2 : 1); k++)
+        {
+            CK(cudaSetDevice(sides[k]->device));
+            CK(cudaStreamSynchronize(sides[k]->stream));
+        }
+    }
+    out[0] = out[1] = 0.0;
+    for (int k = 0; k < (both ? 2 : 1); k++)
+    {
+        float ms = 0.0f;
+        CK(cudaEventElapsedTime(&ms, sides[k]->begin, sides[k]->end));
+        out[k] = static_cast<double>(BYTES) * reps / (ms * 1e-3) / 1e9;
+    }
+}
+
+int main()
+{
+    int count = 0;
+    CK(cudaGetDeviceCount(&count));
+    if (count < 2)
+    {
+        printf("peer_bandwidth needs two GPUs, this machine shows %d: nothing measured\n", count);
+        return 0;
+    }
+    int can01 = 0, can10 = 0;
+    CK(cudaDeviceCanAccessPeer(&can01, 0, 1));
+    CK(cudaDeviceCanAccessPeer(&can10, 1, 0));
+    if (!can01 || !can10)
+    {
+        printf("GPU 0 and GPU 1 cannot map each other's memory: nothing measured\n");
+        return 0;
+    }
+    Side x = make_side(0, 1), y = make_side(1, 0);
+    printf("1 GiB per copy, 5 copies per figure, GB/s per direction\n\n");
+    printf("%-30s %-6s %12s %22s\n", "mover", "", "one direction", "both directions (0 | 1)");
+    for (int how = 0; how < 3; how++)
+    {
+        for (int read = 1; read >= 0; read--)
+        {
+            double one[2], two[2];
+            run(static_cast<Mover>(how), read != 0, x, y, false, one);
+            run(static_cast<Mover>(how), read != 0, x, y, true, two);
+            printf("%-30s %-6s %12.1f %12.1f | %7.1f\n", MOVER_NAMES[how], read ? "read" : "write", one[0], two[0],
+                   two[1]);
+            if (gave_up(x) || gave_up(y))
+            {
+                printf("a bulk copy never completed (bounded wait ran out): stopping\n");
+                return 1;
+            }
+        }
+    }
+    // the last figure was a bulk write of side 0's pattern (1) into side 1's b, and of side 1's (2) into side 0's
+    unsigned char tail0 = 0, tail1 = 0;
+    CK(cudaMemcpy(&tail0, x.b + BYTES - 1, 1, cudaMemcpyDeviceToHost));
+    CK(cudaMemcpy(&tail1, y.b + BYTES - 1, 1, cudaMemcpyDeviceToHost));
+    printf("\nlast byte of each destination: %d and %d (expected 2 and 1)\n", tail0, tail1);
+    return (tail0 == 2 && tail1 == 1) ? 0 : 1;
+}

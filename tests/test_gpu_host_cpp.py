@@ -16,7 +16,7 @@ def test_cpp_host_program_builds():
     from cuda_transformer_b200 import build as lib_build
     lib_build.build()
     exes = build_host_test.build_all()
-    assert [os.path.basename(e) for e in exes] == ["test_amp_host", "test_zero1_host"]
+    assert [os.path.basename(e) for e in exes] == ["test_amp_host", "test_zero1_host", "peer_bandwidth"]
     assert all(os.path.exists(e) for e in exes)
 
 
