@@ -13,6 +13,10 @@ no-op.
     stock:    common dump gpt weights data kernels/*.cu gpt_fast graph checkpoint  + test_X.cu
     b200amp:  the same minus kernels/scaler.cu, kernels/adamw_multi.cu, graph.cu
               plus oracle/link_shim.cu and -lb200amp
+
+The reference's trainer, cuda/train_fast.cu (+ tokenizer/bpe.cpp, Makefile:147-148), is built the
+same two ways, and two token files of seeded random ids in its BPE1 format (cuda/data.cu:30-69) are
+written next to the dump, so that a test can run the whole training program on the library.
 """
 from __future__ import annotations
 
@@ -34,6 +38,8 @@ WEIGHTS_ROUNDTRIP = os.path.join(BIN, "weights_roundtrip")
 DEFAULT_REF = "/root/reference"
 REPLACED = ("kernels/scaler.cu", "kernels/adamw_multi.cu", "graph.cu")
 PROGRAMS = ("test_fast", "test_checkpoint")
+TRAINER = "train_fast"
+TOKENS = os.path.join(OUT, "data", "synth")         # synth_train.bin, synth_val.bin
 
 
 def _nvcc() -> str:
@@ -55,6 +61,34 @@ def _compile(src: str, obj: str, includes) -> None:
 
 def binaries() -> dict:
     return {f"{prog}_{kind}": os.path.join(BIN, f"{prog}_{kind}") for prog in PROGRAMS for kind in ("stock", "b200amp")}
+
+
+def trainer_binaries() -> dict:
+    return {kind: os.path.join(BIN, f"{TRAINER}_{kind}") for kind in ("stock", "b200amp")}
+
+
+def trainer_available() -> bool:
+    return (all(os.path.exists(p) for p in trainer_binaries().values()) and os.path.exists(DUMP)
+            and all(os.path.exists(f"{TOKENS}_{part}.bin") for part in ("train", "val")))
+
+
+def write_tokens() -> str:
+    """BPE1 files (u32 magic 0x31455042, u32 version 1, u32 count, u16 ids; cuda/data.cu:30-69) of
+    seeded random ids below the tiny model's vocabulary: nothing to learn, but every code path of
+    the trainer runs."""
+    import struct
+
+    import numpy as np
+    os.makedirs(os.path.dirname(TOKENS), exist_ok=True)
+    for part, count, seed in (("train", 200_000, 11), ("val", 20_000, 12)):
+        path = f"{TOKENS}_{part}.bin"
+        if os.path.exists(path):
+            continue
+        ids = np.random.default_rng(seed).integers(0, 4098, size=count).astype("<u2")
+        with open(path, "wb") as f:
+            f.write(struct.pack("<III", 0x31455042, 1, count))
+            f.write(ids.tobytes())
+    return TOKENS
 
 
 def available() -> bool:
@@ -117,6 +151,22 @@ def build(ref_root: str = DEFAULT_REF, jobs: int = 8):
             proc = subprocess.run(cmd, capture_output=True, text=True)
             if proc.returncode != 0:
                 raise RuntimeError("link failed: " + " ".join(cmd) + "\n" + proc.stderr[-4000:])
+    # the trainer: cuda/train_fast.cu + tokenizer/bpe.cpp, stock and on the library
+    trainer_obj = os.path.join(OBJ, "train_fast.o")
+    bpe_obj = os.path.join(OBJ, "tokenizer_bpe.o")
+    _compile(os.path.join(cuda, "train_fast.cu"), trainer_obj, includes)
+    _compile(os.path.join(ref_root, "tokenizer", "bpe.cpp"), bpe_obj, includes)
+    stock = [os.path.join(OBJ, r[:-3] + ".o") for r in common]
+    ours = [os.path.join(OBJ, r[:-3] + ".o") for r in common if r not in REPLACED] + [shim_obj]
+    for kind, objs, extra in (("stock", stock, []),
+                              ("b200amp", ours, ["-L", lib_dir, "-lb200amp", "-Xlinker", "-rpath", "-Xlinker",
+                                                 "$ORIGIN/../../../cuda_transformer_b200/lib"])):
+        cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-o", trainer_binaries()[kind], trainer_obj,
+               bpe_obj] + objs + extra
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise RuntimeError("link failed: " + " ".join(cmd) + "\n" + proc.stderr[-4000:])
+    write_tokens()
     # ckpt_roundtrip: the reference's checkpoint reader + writer behind a two-argument command line
     rt_obj = os.path.join(OBJ, "ckpt_roundtrip.o")
     _compile(os.path.join(HERE, "ckpt_roundtrip.cu"), rt_obj, includes)

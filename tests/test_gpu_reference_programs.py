@@ -68,3 +68,90 @@ def test_reference_program_passes_on_the_library(prog, tmp_path):
             assert name in seen, f"optimizer check did not pass: {name}"
     else:
         assert "FAILED" not in ours.stdout or stock.returncode != 0
+
+
+def _train(exe, dump, tokens, out_dir, steps=60, extra=()):
+    cmd = [exe, "-d", dump, "-D", tokens, "-n", str(steps), "-e", "20", "-b", "4", "-c", out_dir] + list(extra)
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    return proc
+
+
+def _log_rows(path):
+    rows = [line.rstrip("\n").split(",") for line in open(path)][1:]
+    # step, train, val, lr, norm, ms, scale, skipped, counted, val_bpb: everything but the time
+    return [[c for i, c in enumerate(r) if i != 5] for r in rows]
+
+
+def test_reference_trainer_runs_on_the_library_and_trains_the_same(tmp_path):
+    """The reference's whole training program (cuda/train_fast.cu: data batches, forward, backward,
+    the optimizer step replayed as a CUDA Graph, evals, the per-step log from the history ring,
+    GPTC checkpoints, weights.bin) linked against the library instead of its own scaler.o,
+    adamw_multi.o and graph.o, on seeded random tokens: 60 steps, then 20 more continued from the
+    checkpoint (--branch). It has to exit 0 and train the same: every logged column (loss, lr, norm,
+    loss scale, skips) and the saved checkpoint and weights equal the stock program's bit for
+    bit if two stock runs are themselves reproducible, else within the spread between them."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(REPO, "oracle"))
+    import build_ref_tests
+    from cuda_transformer_b200 import checkpoint as ck, weights as wt
+    if not build_ref_tests.trainer_available():
+        pytest.skip("oracle/_ref/bin/train_fast_* were not built (no reference checkout at build time)")
+    bins, dump, tokens = build_ref_tests.trainer_binaries(), build_ref_tests.DUMP, build_ref_tests.TOKENS
+    out_dir = os.environ.get("B200AMP_TEST_LOG_DIR") or str(tmp_path)
+    os.makedirs(out_dir, exist_ok=True)
+    runs = {}
+    for tag, exe in (("stock", bins["stock"]), ("stock_again", bins["stock"]), ("b200amp", bins["b200amp"])):
+        d = str(tmp_path / tag)
+        proc = _train(exe, dump, tokens, d)
+        with open(os.path.join(out_dir, f"ref_train_fast_{tag}.log"), "w") as f:
+            f.write(proc.stdout + "\n---- stderr ----\n" + proc.stderr + f"\nexit {proc.returncode}\n")
+        assert proc.returncode == 0, f"{tag}: {proc.stdout[-2000:]}{proc.stderr[-2000:]}"
+        assert "done   best val" in proc.stdout and "saved" in proc.stdout
+        runs[tag] = dict(dir=d, rows=_log_rows(os.path.join(d, "fast_log.csv")),
+                         ckpt=ck.read_checkpoint(os.path.join(d, "ckpt.bin")),
+                         weights=wt.read_weights(os.path.join(d, "weights.bin")))
+    sys.stdout.write(open(os.path.join(out_dir, "ref_train_fast_b200amp.log")).read()[-3000:])
+    stock, again, ours = runs["stock"], runs["stock_again"], runs["b200amp"]
+    assert len(ours["rows"]) == len(stock["rows"]) == 61                # the step-0 eval + 60 steps
+    assert ours["ckpt"].state.step == 60 and bytes(ours["ckpt"].state)[:4] == bytes(stock["ckpt"].state)[:4]
+
+    def spread(a, b):
+        worst = 0.0
+        for ra, rb in zip(a["rows"], b["rows"]):
+            for i, (x, y) in enumerate(zip(ra, rb)):
+                if x == y:
+                    continue
+                assert i in (1, 2, 4, 8), f"columns other than the losses and the norm differ: {ra} / {rb}"
+                worst = max(worst, abs(float(x) - float(y)) / max(abs(float(y)), 1e-12))
+        for name in ("params", "m", "v"):
+            x, y = getattr(a["ckpt"], name), getattr(b["ckpt"], name)
+            worst = max(worst, float(np.max(np.abs(x - y))) / max(float(np.max(np.abs(y))), 1e-30))
+        return worst
+
+    reproducible = spread(stock, again) == 0.0
+    if reproducible:
+        assert ours["rows"] == stock["rows"], "the training log differs from the stock program's"
+        assert bytes(ours["ckpt"].state) == bytes(stock["ckpt"].state)
+        for name in ("params", "m", "v"):
+            assert np.array_equal(getattr(ours["ckpt"], name), getattr(stock["ckpt"], name)), name
+        assert np.array_equal(ours["weights"].params, stock["weights"].params)
+    else:
+        assert spread(ours, stock) <= max(4 * spread(stock, again), 1e-5)
+    print("stock runs reproducible:", reproducible, "| library vs stock spread:", spread(ours, stock))
+    # continue each run from its own checkpoint for 20 more steps (--branch: the checkpoint's weights,
+    # AdamW state, step and settings, cuda/train_fast.cu:84-86)
+    for tag in ("stock", "b200amp"):
+        branch_dir = runs[tag]["dir"] + "_branch"
+        cmd = [bins[tag], "--branch", os.path.join(runs[tag]["dir"], "ckpt.bin"), "-n", "80", "-e", "20", "-c",
+               branch_dir]
+        proc = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+        with open(os.path.join(out_dir, f"ref_train_fast_{tag}_branch.log"), "w") as f:
+            f.write(proc.stdout + "\n---- stderr ----\n" + proc.stderr + f"\nexit {proc.returncode}\n")
+        assert proc.returncode == 0, f"{tag} branch: {proc.stdout[-2000:]}{proc.stderr[-2000:]}"
+        runs[tag]["resumed"] = ck.read_checkpoint(os.path.join(branch_dir, "ckpt.bin"))
+    a, b = runs["b200amp"]["resumed"], runs["stock"]["resumed"]
+    assert a.state.step == 80 and b.state.step == 80 and a.state.skipped == b.state.skipped
+    if reproducible:
+        assert bytes(a.state) == bytes(b.state) and np.array_equal(a.params, b.params)
+    # and the library's file is one our own reader, writer and the weights export agree on
+    assert wt.read_weights(os.path.join(runs["b200amp"]["dir"] + "_branch", "weights.bin")).params.size == a.params.size
