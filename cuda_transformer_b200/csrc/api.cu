@@ -67,7 +67,7 @@ int sm_count()
 
 Tunables &tunables()
 {
-    static Tunables t = {4, 2, 1, 256, 0, 6, 0, 8, 0};   // measured best on B200 at the 1.3 B arena
+    static Tunables t = {4, 2, 1, 256, 0, 6, 0, 8, 0, 16};   // measured best on B200 at the 1.3 B arena
     return t;
 }
 
@@ -88,6 +88,7 @@ static const Knob KNOBS[] = {
     {"pass2_test_starve", &Tunables::pass2_test_starve, 0, 1},
     {"rs_blocks_per_sm", &Tunables::rs_blocks_per_sm, 1, 32},
     {"ag_blocks_per_sm", &Tunables::ag_blocks_per_sm, 0, 32},
+    {"bridge_blocks_per_sm", &Tunables::bridge_blocks_per_sm, 1, 32},
 };
 
 } // namespace b200amp

@@ -32,6 +32,7 @@ struct Tunables
     int pass2_test_starve;      // test hook of the staged kernel: 1 makes one barrier wait run out (see pass2.cu)
     int rs_blocks_per_sm;       // resident CTAs per SM of the fused reduce-scatter + pass 1
     int ag_blocks_per_sm;       // resident CTAs per SM of the fused pass 2 + all-gather, 0 = by rank count
+    int bridge_blocks_per_sm;   // CTAs per SM asked for by the fp32 -> fp16 bridge (cast + pass 1)
 };
 Tunables &tunables();
 
