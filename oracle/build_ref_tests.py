@@ -46,11 +46,12 @@ def _nvcc() -> str:
     return shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
 
 
-def _compile(src: str, obj: str, includes) -> None:
+def _compile(src: str, obj: str, includes, defines=()) -> None:
     if os.path.exists(obj) and os.path.getmtime(obj) >= os.path.getmtime(src):
         return
     os.makedirs(os.path.dirname(obj), exist_ok=True)
     cmd = [_nvcc(), "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-DFP16"]
+    cmd += [f"-D{d}" for d in defines]
     for inc in includes:
         cmd += ["-I", inc]
     cmd += ["-c", src, "-o", obj]
@@ -64,7 +65,9 @@ def binaries() -> dict:
 
 
 def trainer_binaries() -> dict:
-    return {kind: os.path.join(BIN, f"{TRAINER}_{kind}") for kind in ("stock", "b200amp")}
+    """stock; b200amp = the compat link shim (the reference's results bit for bit); b200amp_native = the
+    link shim built with -DB200AMP_SHIM_NATIVE (bridge + fp16-arena step under the same three calls)."""
+    return {kind: os.path.join(BIN, f"{TRAINER}_{kind}") for kind in ("stock", "b200amp", "b200amp_native")}
 
 
 def trainer_available() -> bool:
@@ -158,9 +161,13 @@ def build(ref_root: str = DEFAULT_REF, jobs: int = 8):
     _compile(os.path.join(ref_root, "tokenizer", "bpe.cpp"), bpe_obj, includes)
     stock = [os.path.join(OBJ, r[:-3] + ".o") for r in common]
     ours = [os.path.join(OBJ, r[:-3] + ".o") for r in common if r not in REPLACED] + [shim_obj]
-    for kind, objs, extra in (("stock", stock, []),
-                              ("b200amp", ours, ["-L", lib_dir, "-lb200amp", "-Xlinker", "-rpath", "-Xlinker",
-                                                 "$ORIGIN/../../../cuda_transformer_b200/lib"])):
+    native_shim_obj = os.path.join(OBJ, "link_shim_native.o")
+    _compile(os.path.join(HERE, "link_shim.cu"), native_shim_obj, includes + [os.path.join(REPO, "include")],
+             defines=("B200AMP_SHIM_NATIVE",))
+    native = [o for o in ours if o != shim_obj] + [native_shim_obj]
+    with_lib = ["-L", lib_dir, "-lb200amp", "-Xlinker", "-rpath", "-Xlinker",
+                "$ORIGIN/../../../cuda_transformer_b200/lib"]
+    for kind, objs, extra in (("stock", stock, []), ("b200amp", ours, with_lib), ("b200amp_native", native, with_lib)):
         cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-o", trainer_binaries()[kind], trainer_obj,
                bpe_obj] + objs + extra
         proc = subprocess.run(cmd, capture_output=True, text=True)

@@ -51,6 +51,10 @@ void begin_step(StepState *st, cudaStream_t s)
     SHIM_CHECK(b200amp_begin_step(abi(st), s));
 }
 
+#ifndef B200AMP_SHIM_NATIVE
+
+// ---- compat: the reference's arguments and results, bit for bit
+
 void unscale_and_norm(float *grads, long long n, StepState *st, float *partial, cudaStream_t s)
 {
     SHIM_CHECK(b200amp_unscale_and_norm_f32(grads, n, abi(st), partial, s));
@@ -71,6 +75,84 @@ void adamw_multi(float *params, floatX *params_x, const float *grads, float *m, 
                                        reinterpret_cast<const b200amp_tensor_info *>(tensors), ntensors,
                                        reinterpret_cast<const b200amp_step_state *>(st), beta1, beta2, eps, s));
 }
+
+#else
+
+// ---- native (-DB200AMP_SHIM_NATIVE): the same three calls routed onto the fp16-arena step.
+// The reference's backward pass leaves loss-scaled fp32 gradients in its arena; unscale_and_norm
+// becomes the bridge (round to fp16 into an arena this shim keeps, pass 1 on the rounded values,
+// fp32 arena cleared behind it), finalize_step the finalize on the bridge's sums, adamw_multi the
+// native pass 2 on the fp16 arena. 10 + 28 B/param instead of 8 + 30 + the 4 B/param memset, and
+// the gradients the optimizer sees are rounded to fp16 first, so a run agrees with the stock
+// program to fp16 rounding of the gradients, not bit for bit; the fp32 arena is NOT unscaled in
+// place (test_fast reads it back, so the test programs use the compat shim). For train_fast.
+
+struct NativeArena
+{
+    const float *grads32 = nullptr;         // which fp32 arena this belongs to
+    long long n = 0;
+    void *grads16 = nullptr;
+    void *workspace = nullptr;
+};
+
+static NativeArena g_arena;                 // the reference's programs hold one model
+
+// Called inside train_fast's graph capture the first time (its first step IS the captured one), so
+// the allocation asks for relaxed capture rules on this thread for its duration; the clearing of
+// the workspace is stream-ordered and simply becomes part of the graph.
+static NativeArena &arena_for(const float *grads32, long long n, cudaStream_t s)
+{
+    if (g_arena.grads32 == grads32 && g_arena.n == n)
+    {
+        return g_arena;
+    }
+    if (g_arena.grads32 != nullptr)
+    {
+        fprintf(stderr, "link shim (native): a second gradient arena appeared; this shim serves one model\n");
+        exit(1);
+    }
+    cudaStreamCaptureMode mode = cudaStreamCaptureModeRelaxed;
+    CUDA_CHECK(cudaThreadExchangeStreamCaptureMode(&mode));
+    CUDA_CHECK(cudaMalloc(&g_arena.grads16, static_cast<size_t>(n) * 2));
+    CUDA_CHECK(cudaMalloc(&g_arena.workspace, b200amp_workspace_bytes()));
+    CUDA_CHECK(cudaThreadExchangeStreamCaptureMode(&mode));
+    SHIM_CHECK(b200amp_workspace_init(g_arena.workspace, s));
+    g_arena.grads32 = grads32;
+    g_arena.n = n;
+    return g_arena;
+}
+
+void unscale_and_norm(float *grads, long long n, StepState *st, float *, cudaStream_t s)
+{
+    NativeArena &a = arena_for(grads, n, s);
+    SHIM_CHECK(b200amp_cast_pass1_f32(grads, a.grads16, n, /*clear_source=*/1, abi(st), a.workspace, nullptr, nullptr,
+                                      0, s));
+}
+
+void finalize_step(StepState *st, const float *, ScheduleConfig cfg, StepState *history, int history_len,
+                   cudaStream_t s)
+{
+    if (g_arena.workspace == nullptr)
+    {
+        fprintf(stderr, "link shim (native): finalize_step before unscale_and_norm\n");
+        exit(1);
+    }
+    // the first 16 bytes of the workspace are {sum of squares, flag}: one "rank"
+    SHIM_CHECK(b200amp_finalize_sums(abi(st), static_cast<const double *>(g_arena.workspace), 1,
+                                     reinterpret_cast<const b200amp_schedule *>(&cfg), abi(history), history_len, s));
+}
+
+void adamw_multi(float *params, floatX *params_x, const float *grads, float *m, float *v, long long n,
+                 const TensorInfo *tensors, int ntensors, const StepState *st, float beta1, float beta2, float eps,
+                 cudaStream_t s)
+{
+    NativeArena &a = arena_for(grads, n, s);
+    SHIM_CHECK(b200amp_pass2_f16(params, m, v, a.grads16, params_x, n, 0,
+                                 reinterpret_cast<const b200amp_tensor_info *>(tensors), ntensors,
+                                 reinterpret_cast<const b200amp_step_state *>(st), beta1, beta2, eps, s));
+}
+
+#endif
 
 double lr_on_gpu(int step, ScheduleConfig cfg)
 {

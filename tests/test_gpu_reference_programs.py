@@ -155,3 +155,50 @@ def test_reference_trainer_runs_on_the_library_and_trains_the_same(tmp_path):
         assert bytes(a.state) == bytes(b.state) and np.array_equal(a.params, b.params)
     # and the library's file is one our own reader, writer and the weights export agree on
     assert wt.read_weights(os.path.join(runs["b200amp"]["dir"] + "_branch", "weights.bin")).params.size == a.params.size
+
+
+def test_reference_trainer_on_the_native_step_agrees_to_fp16_rounding_of_the_gradients(tmp_path):
+    """The same trainer with the link shim built -DB200AMP_SHIM_NATIVE: its three optimizer calls
+    become the fp32 -> fp16 bridge (pass 1 folded in, fp32 arena cleared behind it), the finalize
+    on the bridge's sums and the native pass 2 on an fp16 gradient arena: the 30 B/param step
+    (+ the bridge) under the reference's unmodified training program, replayed as a CUDA Graph.
+    The optimizer then sees gradients rounded to fp16 (relative 5e-4 per element), so the run is
+    held to the stock program's within that: same skip decisions and loss scale, losses within
+    1e-3 relative, m and v within 1e-3 of their largest value. Parameters are held to 1e-3 of
+    the largest: AdamW divides by sqrt(v), so an element whose gradient is so small that its fp16
+    value has only a few significant bits moves by up to the learning rate per step either way
+    (the reference notes the same about near-zero gradients, reference/dump.py:54-65)."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(REPO, "oracle"))
+    import build_ref_tests
+    from cuda_transformer_b200 import checkpoint as ck
+    bins = build_ref_tests.trainer_binaries()
+    if not build_ref_tests.trainer_available() or not os.path.exists(bins["b200amp_native"]):
+        pytest.skip("oracle/_ref/bin/train_fast_* were not built (no reference checkout at build time)")
+    dump, tokens = build_ref_tests.DUMP, build_ref_tests.TOKENS
+    out_dir = os.environ.get("B200AMP_TEST_LOG_DIR") or str(tmp_path)
+    os.makedirs(out_dir, exist_ok=True)
+    runs = {}
+    for tag in ("stock", "b200amp_native"):
+        d = str(tmp_path / tag)
+        proc = _train(bins[tag], dump, tokens, d)
+        with open(os.path.join(out_dir, f"ref_train_fast_{tag}_60.log"), "w") as f:
+            f.write(proc.stdout + "\n---- stderr ----\n" + proc.stderr + f"\nexit {proc.returncode}\n")
+        assert proc.returncode == 0, f"{tag}: {proc.stdout[-2000:]}{proc.stderr[-2000:]}"
+        runs[tag] = dict(rows=_log_rows(os.path.join(d, "fast_log.csv")),
+                         ckpt=ck.read_checkpoint(os.path.join(d, "ckpt.bin")))
+    stock, ours = runs["stock"], runs["b200amp_native"]
+    assert len(ours["rows"]) == len(stock["rows"]) == 61
+    for ra, rb in zip(ours["rows"][1:], stock["rows"][1:]):
+        assert ra[0] == rb[0] and ra[3] == rb[3] and ra[5:8] == rb[5:8], (ra, rb)    # step, lr, scale, skipped, counted
+        assert abs(float(ra[1]) - float(rb[1])) <= 1e-3 * abs(float(rb[1])), (ra, rb)      # train loss
+        assert abs(float(ra[4]) - float(rb[4])) <= 2e-3 * abs(float(rb[4])), (ra, rb)      # gradient norm
+    a, b = ours["ckpt"], stock["ckpt"]
+    assert (a.state.step, a.state.adam_t, a.state.skipped, a.state.loss_scale) == \
+           (b.state.step, b.state.adam_t, b.state.skipped, b.state.loss_scale)
+    worst = {}
+    for name in ("params", "m", "v"):
+        x, y = getattr(a, name), getattr(b, name)
+        worst[name] = float(np.max(np.abs(x - y))) / float(np.max(np.abs(y)))
+    print("native trainer vs stock after 60 steps, max |diff| / max |ref|:", worst)
+    assert worst["params"] <= 1e-3 and worst["m"] <= 1e-3 and worst["v"] <= 1e-3
