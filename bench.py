@@ -372,6 +372,29 @@ def run_gpu(args) -> dict:
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
 
+    graph_replay = None
+    if world == 1:
+        # The same step as ONE CUDA-graph launch (how the reference's trainer replays it,
+        # cuda/train_fast.cu:720-730): per-replay times by events, median reported.
+        side = torch.cuda.Stream(device=dev)
+        graph = amp.CudaGraph()
+        torch.cuda.synchronize()
+        with torch.cuda.stream(side):
+            graph.capture(side, lambda: opt.optimizer_step(side))
+            for _ in range(3):
+                graph.launch(side)
+            marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+            marks[0].record(side)
+            for k in range(args.steps):
+                graph.launch(side)
+                marks[k + 1].record(side)
+        side.synchronize()
+        times = sorted(marks[k].elapsed_time(marks[k + 1]) for k in range(args.steps))
+        graph_replay = {"median_ms": statistics.median(times), "min_ms": times[0], "max_ms": times[-1],
+                        "replays": args.steps}
+        if opt.read_state().skipped != 0:
+            raise SystemExit("a graph replay was skipped")
+
     skipped_step = None
     if world == 1:
         # A skipped step (an inf among the gradients) moves 2 B/param: pass 1 reads the arena, pass 2
@@ -432,6 +455,8 @@ def run_gpu(args) -> dict:
         line["phases"] = phases
     if skipped_step:
         line["skipped_step"] = skipped_step
+    if graph_replay:
+        line["graph_replay"] = graph_replay
     line["roofline"]["traffic"] = PASS2_DRAM_BYTES_PER_PARAM_NCU * n_local
     line["roofline"]["traffic_source"] = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on the "
                                           "gpt2-small arena (profiles/), scaled by the element count")
