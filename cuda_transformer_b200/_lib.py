@@ -47,7 +47,23 @@ class TensorInfo(C.Structure):
     _fields_ = [("offset", C.c_longlong), ("count", C.c_longlong), ("decay", C.c_int)]
 
 
+class Zero1Sync(C.Structure):
+    """b200amp_zero1_sync: every rank's block of flag words as mapped in this process, and the
+    number of polls after which a wait on another rank gives up (0 = the library's default)."""
+    _fields_ = [("block_by_rank", C.c_void_p * 8), ("wait_limit", C.c_uint)]
+
+
+class DecayRuns(C.Structure):
+    """b200amp_decay_runs: the tensor table merged into runs of equal decay flag."""
+    _fields_ = [("first4", C.c_uint * 256), ("nruns", C.c_int), ("flag0", C.c_int)]
+
+
+ZERO1_SYNC_BYTES = 256
+SYNC_SIGNAL, SYNC_WAIT, SYNC_ADVANCE = 1, 2, 4
+PHASE_GRADS, PHASE_PAIRS, PHASE_WEIGHTS = 0, 1, 2
+
 assert C.sizeof(StepState) == 60 and C.sizeof(ScheduleConfig) == 44 and C.sizeof(TensorInfo) == 24
+assert C.sizeof(Zero1Sync) == 72
 
 _P = C.c_void_p
 _LL = C.c_longlong
@@ -75,8 +91,20 @@ PROTOTYPES = {
     "b200amp_finalize_sums": (_I, [_P, _P, _I, C.POINTER(ScheduleConfig), _P, _I, _P]),
     "b200amp_pass1_finalize_f16": (_I, [_P, _LL, _P, _P, C.POINTER(ScheduleConfig), _P, _I, _P]),
     "b200amp_pass2_f16": (_I, [_P, _P, _P, _P, _P, _LL, _LL, _P, _I, _P, _F, _F, _F, _P]),
+    "b200amp_decay_runs_build": (_I, [_P, _I, C.POINTER(DecayRuns)]),
+    "b200amp_pass2_f16_runs": (_I, [_P, _P, _P, _P, _P, _LL, _LL, C.POINTER(DecayRuns), _P, _F, _F, _F, _P]),
     "b200amp_rs_pass1_f16": (_I, [_P, _I, _I, _P, _LL, _P, _P, _P, _P]),
     "b200amp_pass2_ag_f16": (_I, [_P, _P, _P, _P, _P, _I, _LL, _LL, _P, _I, _P, _F, _F, _F, _P]),
+    "b200amp_rs_pass1_f16_part": (_I, [_P, _I, _I, _P, _LL, _I, _I, _I, _P, _P, _P, _P]),
+    "b200amp_pass1_partition": (_I, [_LL, C.POINTER(_I), C.POINTER(_LL)]),
+    "b200amp_copy_async": (_I, [_P, _P, _LL, _P]),
+    "b200amp_zero1_sync_init": (_I, [_P, _P]),
+    "b200amp_zero1_sync_read": (_I, [_P, C.POINTER(C.c_uint), C.POINTER(C.c_uint)]),
+    "b200amp_zero1_barrier": (_I, [C.POINTER(Zero1Sync), _I, _I, _I, _I, _P]),
+    "b200amp_rs_pass1_f16_sync": (_I, [_P, _I, _I, _P, _LL, _P, _P, _P, C.POINTER(Zero1Sync), _P]),
+    "b200amp_finalize_sums_sync": (_I, [_P, _P, _I, _I, C.POINTER(ScheduleConfig), _P, _I, C.POINTER(Zero1Sync), _P]),
+    "b200amp_rs_pass1_f16_ce": (_I, [_P, _I, _I, _P, _P, _LL, _I, _P, _P, _P, C.POINTER(Zero1Sync), _P]),
+    "b200amp_pass2_ag_f16_ce": (_I, [_P, _P, _P, _P, _P, _I, _I, _LL, _LL, _P, _I, _P, _F, _F, _F, _I, _P]),
     "b200amp_step_f16": (_I, [_P, _P, _P, _P, _P, _LL, _P, _I, _P, _P, C.POINTER(ScheduleConfig), _P, _I,
                               _F, _F, _F, _P]),
     "b200amp_graph_begin_capture": (_I, [_P]),

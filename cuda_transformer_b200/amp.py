@@ -27,7 +27,7 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 
 from . import _lib
-from ._lib import B200AmpError, ScheduleConfig, StepState, TensorInfo, check
+from ._lib import B200AmpError, DecayRuns, ScheduleConfig, StepState, TensorInfo, Zero1Sync, check
 from .layout import ParamSlot, padded, shard_range, tensor_table
 
 __all__ = [
@@ -36,6 +36,9 @@ __all__ = [
     "cast_to_x", "CudaGraph", "AmpOptimizer", "Zero1Step", "ShardedAmpOptimizer", "make_schedule",
     "pass1_f16", "pass1_f16_static", "cast_pass1_f32", "pass1_finalize_f16", "rs_pass1_f16", "pass2_ag_f16",
     "FusedZero1Optimizer", "finalize_sums", "pass2_f16", "step_f16", "check_tensor_table",
+    "pass1_partition", "rs_pass1_f16_part", "copy_async", "rs_pass1_f16_ce", "pass2_ag_f16_ce",
+    "DecayRuns", "decay_runs_build", "pass2_f16_runs", "Zero1Sync", "make_sync", "zero1_sync_init", "zero1_sync_read", "zero1_barrier", "rs_pass1_f16_sync",
+    "finalize_sums_sync", "device_error", "RankWaitError",
 ]
 
 
@@ -155,6 +158,23 @@ def pass2_f16(master, m, v, grads16, weights16, n: int, arena_offset: int, tenso
                                         _stream(stream)))
 
 
+def decay_runs_build(table: Sequence[Tuple[int, int, int]]) -> DecayRuns:
+    """The (offset, count, decay) rows merged into runs of equal decay flag, for pass2_f16_runs.
+    Raises B200AmpError (status ERR_LIMIT) when the table has more than 256 runs."""
+    arr = (TensorInfo * max(1, len(table)))(*[TensorInfo(o, c, d) for o, c, d in table])
+    runs = DecayRuns()
+    check(_lib.load().b200amp_decay_runs_build(C.cast(arr, C.c_void_p), len(table), C.byref(runs)))
+    return runs
+
+
+def pass2_f16_runs(master, m, v, grads16, weights16, n: int, arena_offset: int, runs: DecayRuns, st,
+                   beta1: float, beta2: float, eps: float, stream=None) -> None:
+    """pass2_f16 with the decay runs passed as a kernel parameter (no table in device memory)."""
+    check(_lib.load().b200amp_pass2_f16_runs(_ptr(master), _ptr(m), _ptr(v), _ptr(grads16), _ptr(weights16), n,
+                                             arena_offset, C.byref(runs), _ptr(st), beta1, beta2, eps,
+                                             _stream(stream)))
+
+
 def _pointer_array(pointers: Sequence[int]):
     return (C.c_void_p * len(pointers))(*[C.c_void_p(int(p)) for p in pointers])
 
@@ -177,6 +197,104 @@ def pass2_ag_f16(master, m, v, reduced16, weights16_by_rank: Sequence[int], n: i
                                            _pointer_array(weights16_by_rank), len(weights16_by_rank), n,
                                            arena_offset, _ptr(tensors), ntensors, _ptr(st), beta1, beta2, eps,
                                            _stream(stream)))
+
+
+def pass1_partition(n: int):
+    """(virtual blocks, elements per virtual block) of the fixed partition pass 1 sums a range of
+    n elements over."""
+    vblocks, per = C.c_int(), C.c_longlong()
+    check(_lib.load().b200amp_pass1_partition(n, C.byref(vblocks), C.byref(per)))
+    return vblocks.value, per.value
+
+
+def rs_pass1_f16_part(grads16_by_rank: Sequence[int], my_rank: int, reduced16, n: int, vblock_first: int,
+                      vblock_count: int, last_part: bool, st, workspace,
+                      pair_table_by_rank: Optional[Sequence[int]] = None, stream=None) -> None:
+    """rs_pass1_f16 on the virtual blocks vblock_first .. vblock_first + vblock_count - 1 of the slice."""
+    tables = _pointer_array(pair_table_by_rank) if pair_table_by_rank is not None else None
+    check(_lib.load().b200amp_rs_pass1_f16_part(_pointer_array(grads16_by_rank), len(grads16_by_rank), my_rank,
+                                                _ptr(reduced16), n, vblock_first, vblock_count,
+                                                1 if last_part else 0, _ptr(st), _ptr(workspace), tables,
+                                                _stream(stream)))
+
+
+def copy_async(dst, src, nbytes: int, stream=None) -> None:
+    """Copy-engine transfer between two device pointers of this process (peer mappings included)."""
+    check(_lib.load().b200amp_copy_async(_ptr(dst), _ptr(src), nbytes, _stream(stream)))
+
+
+# ---- ordering between one-process-per-GPU ranks (include/b200amp.h, "owned by the library")
+
+def make_sync(block_by_rank: Sequence[int], wait_limit: int = 0) -> Zero1Sync:
+    """block_by_rank[r]: rank r's block of flag words as a device pointer of THIS process."""
+    sync = Zero1Sync()
+    for r, p in enumerate(block_by_rank):
+        sync.block_by_rank[r] = int(p)
+    sync.wait_limit = wait_limit
+    return sync
+
+
+def zero1_sync_init(block, stream=None) -> None:
+    check(_lib.load().b200amp_zero1_sync_init(_ptr(block), _stream(stream)))
+
+
+def zero1_sync_read(block) -> Tuple[int, int]:
+    """(steps completed, error word) of a rank's own block; synchronous."""
+    steps, error = C.c_uint(), C.c_uint()
+    check(_lib.load().b200amp_zero1_sync_read(_ptr(block), C.byref(steps), C.byref(error)))
+    return steps.value, error.value
+
+
+def zero1_barrier(sync: Zero1Sync, nranks: int, my_rank: int, phase: int, what: int, stream=None) -> None:
+    check(_lib.load().b200amp_zero1_barrier(C.byref(sync), nranks, my_rank, phase, what, _stream(stream)))
+
+
+def rs_pass1_f16_sync(grads16_by_rank: Sequence[int], my_rank: int, reduced16, n: int, st, workspace,
+                      pair_table_by_rank: Sequence[int], sync: Zero1Sync, stream=None) -> None:
+    check(_lib.load().b200amp_rs_pass1_f16_sync(_pointer_array(grads16_by_rank), len(grads16_by_rank), my_rank,
+                                                _ptr(reduced16), n, _ptr(st), _ptr(workspace),
+                                                _pointer_array(pair_table_by_rank), C.byref(sync), _stream(stream)))
+
+
+def finalize_sums_sync(st, sums, nranks: int, my_rank: int, cfg: ScheduleConfig, sync: Zero1Sync, history=None,
+                       history_len: int = 0, stream=None) -> None:
+    check(_lib.load().b200amp_finalize_sums_sync(_ptr(st), _ptr(sums), nranks, my_rank, C.byref(cfg), _ptr(history),
+                                                 history_len, C.byref(sync), _stream(stream)))
+
+
+def rs_pass1_f16_ce(grads16_by_rank: Sequence[int], my_rank: int, staging16, reduced16, n: int, pieces: int, st,
+                    workspace, pair_table_by_rank: Optional[Sequence[int]] = None,
+                    sync: Optional[Zero1Sync] = None, stream=None) -> None:
+    """Reduce-scatter + pass 1 with the peers' slices pulled by the copy engines into staging16
+    ((nranks - 1) * n fp16 values, local), piece by piece, while earlier pieces are reduced."""
+    tables = _pointer_array(pair_table_by_rank) if pair_table_by_rank is not None else None
+    check(_lib.load().b200amp_rs_pass1_f16_ce(_pointer_array(grads16_by_rank), len(grads16_by_rank), my_rank,
+                                              _ptr(staging16), _ptr(reduced16), n, pieces, _ptr(st),
+                                              _ptr(workspace), tables,
+                                              C.byref(sync) if sync is not None else None, _stream(stream)))
+
+
+def pass2_ag_f16_ce(master, m, v, reduced16, weights16_by_rank: Sequence[int], my_rank: int, n: int,
+                    arena_offset: int, tensors, ntensors: int, st, beta1: float, beta2: float, eps: float,
+                    pieces: int, stream=None) -> None:
+    """Pass 2 + all-gather with every piece of fp16 weights pushed to the peers by the copy
+    engines while pass 2 runs on the next piece."""
+    check(_lib.load().b200amp_pass2_ag_f16_ce(_ptr(master), _ptr(m), _ptr(v), _ptr(reduced16),
+                                              _pointer_array(weights16_by_rank), len(weights16_by_rank), my_rank, n,
+                                              arena_offset, _ptr(tensors), ntensors, _ptr(st), beta1, beta2, eps,
+                                              pieces, _stream(stream)))
+
+
+def device_error() -> int:
+    """Bit mask of what gave up a bounded wait on the current device since the last call (1: a bulk
+    copy of the staged pass 2, 2: a wait on another rank); reading clears it. Synchronises."""
+    out = C.c_int()
+    check(_lib.load().b200amp_device_error(C.byref(out)))
+    return out.value
+
+
+class RankWaitError(B200AmpError):
+    """A kernel of the ZeRO-1 step stopped waiting for another rank. The step was not applied."""
 
 
 def step_f16(master, m, v, grads16, weights16, n: int, tensors, ntensors: int, st, workspace,
@@ -308,16 +426,43 @@ class AmpOptimizer:
         with torch.cuda.device(self.device):
             cast_to_x(self.weights16, self.master, self.n)
 
-    def optimizer_step(self, stream=None) -> None:
-        """The two launches of the step (the place of cuda/gpt_fast.cu:438-450)."""
+    def decay_runs(self) -> DecayRuns:
+        """The tensor table merged into runs of equal decay flag (built once, on the host)."""
+        if getattr(self, "_runs", None) is None:
+            table = list(tensor_table(self.slots))
+            if self.n > self.n_params:
+                table.append((self.n_params, self.n - self.n_params, 0))
+            self._runs = decay_runs_build(table)
+        return self._runs
+
+    def optimizer_step(self, stream=None, pass2: str = "table") -> None:
+        """The two launches of the step (the place of cuda/gpt_fast.cu:438-450). pass2 = "runs"
+        hands the decay flags to pass 2 as a kernel parameter (tables of at most 256 runs)
+        instead of the table in device memory; the results are the same bits."""
         with torch.cuda.device(self.device):
+            if pass2 == "runs":
+                pass1_finalize_f16(self.grads16, self.n, self.state, self.workspace, self.sched, self.history,
+                                   self.history_len, stream)
+                pass2_f16_runs(self.master, self.m, self.v, self.grads16, self.weights16, self.n, 0,
+                               self.decay_runs(), self.state, self.beta1, self.beta2, self.eps, stream)
+                return
             step_f16(self.master, self.m, self.v, self.grads16, self.weights16, self.n, self.tensors,
                      self.ntensors, self.state, self.workspace, self.sched, self.history, self.history_len,
                      self.beta1, self.beta2, self.eps, stream)
 
     def read_state(self) -> StepState:
-        """Sync + D2H of the 60-byte state (cuda/gpt_fast.cu:461-467)."""
+        """Sync + D2H of the 60-byte state (cuda/gpt_fast.cu:461-467). When the staged pass 2 is
+        selected (tuning knob pass2_variant = 1) its give-up flag is checked here too: a launch
+        that stopped waiting for a bulk copy has updated some tiles only, and the caller must not
+        go on with that state."""
         raw = bytes(self.state.cpu().numpy().tobytes())
+        variant = C.c_int()
+        check(self.lib.b200amp_tune_get(b"pass2_variant", C.byref(variant)))
+        if variant.value == 1:
+            with torch.cuda.device(self.device):
+                if device_error() & 1:
+                    raise B200AmpError(_lib.ERR_CUDA, "the staged pass 2 gave up waiting for a bulk copy: master, m "
+                                       "and v are partly updated; restore them from a checkpoint")
         return StepState.from_buffer_copy(raw)
 
     def read_history(self) -> List[StepState]:
@@ -493,33 +638,53 @@ class ShardedAmpOptimizer(Zero1Step):
 
 
 class FusedZero1Optimizer(ShardedAmpOptimizer):
-    """ZeRO-1 with the collectives folded into the two passes (b200amp_rs_pass1_f16,
-    b200amp_pass2_ag_f16) instead of NCCL calls around them.
+    """ZeRO-1 with the collectives folded into the two passes instead of NCCL calls around them,
+    and the ordering between the ranks done by the library's own flag words.
 
-    The fp16 gradient arena, the fp16 weight arena and the table of {sum, flag} pairs are
-    allocated as symmetric memory (torch.distributed._symmetric_memory): every rank's buffers
-    are mapped into every process, so a kernel reads a peer's gradients and writes a peer's
-    weights with ordinary loads and stores over NVLink. One step on each rank, all on one stream:
+    The fp16 gradient arena, the fp16 weight arena, the table of {sum, flag} pairs and one
+    256-byte block of flag words are allocated as symmetric memory
+    (torch.distributed._symmetric_memory, used for the allocation and the mapping only): every
+    rank's buffers are mapped into every process, so a kernel reads a peer's gradients and writes a
+    peer's weights with ordinary loads and stores over NVLink. Multicast binding is switched off
+    for these allocations (the kernels use no multimem instruction). One step on each rank, four
+    launches on one stream, nothing on the host in between:
 
-        barrier                      every rank's gradients are in its arena
-        rs_pass1                     pull + average my slice, norm partials, pairs -> every table
-        barrier                      every pair has landed in every table
-        finalize_sums                replicated, rank-ordered: identical state bits everywhere
-        pass2_ag                     AdamW on my slice, fp16 weights -> every arena
-        barrier                      every slice has landed in every weight arena
+        rs_pass1 (sync)     every CTA announces "my gradients are ready" and waits for every
+                            rank's; pull + average my slice, norm partials, pair -> every table;
+                            the last CTA announces "my pair is written"
+        finalize (sync)     waits for every rank's pair; replicated, rank-ordered: identical
+                            state bits everywhere
+        pass2_ag            AdamW on my slice, fp16 weights -> every arena
+        barrier             announces "my weights have landed", waits for every rank's, advances
+                            the step counter that lives in the flag block
 
-    The barriers are the symmetric-memory handle's (signal pads, stream-ordered, with a
-    timeout); the kernels themselves never wait on another GPU. The averaged gradient is
-    rounded to fp16 once from an fp32 sum, so it is at least as accurate as an fp16 NCCL
-    reduction; norm and flag are taken on exactly the stored averaged values.
+    mover="ce" moves the NVLink bytes with the copy engines instead (b200amp_rs_pass1_f16_ce,
+    b200amp_pass2_ag_f16_ce; `ce_use` picks the phases, `pieces` the pipelining); the results are
+    the same bits.
+
+    Every wait is bounded (about a second, `wait_limit` polls). A rank that never shows up makes
+    the others' kernels return without applying the step; read_state() then raises
+    RankWaitError naming the phase and the missing rank. The averaged gradient is rounded to
+    fp16 once from an fp32 sum, so it is at least as accurate as an fp16 NCCL reduction; norm and
+    flag are taken on exactly the stored averaged values.
     """
 
-    BARRIER_TIMEOUT_MS = 10_000
+    PHASE_NAMES = ("gradients ready", "pairs written", "weights written")
 
     def __init__(self, slots: List[ParamSlot], cfg: ScheduleConfig, eps: float = 1e-8,
-                 loss_scale: float = 65536.0, history_len: int = 256, device=None, group=None):
+                 loss_scale: float = 65536.0, history_len: int = 256, device=None, group=None,
+                 mover: str = "sm", ce_use: str = "rs+ag", pieces: int = 4, wait_limit: int = 0):
+        import os
         import torch.distributed as dist
+        # the kernels use plain peer loads and stores: do not bind the arenas to an NVLink multicast
+        # object (a rank that dies while bound to one can fault its peers' GPUs)
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
+        if mover not in ("sm", "ce"):
+            raise ValueError(f"mover = {mover!r}: expected 'sm' or 'ce'")
+        if ce_use not in ("rs", "ag", "rs+ag"):
+            raise ValueError(f"ce_use = {ce_use!r}: expected 'rs', 'ag' or 'rs+ag'")
+        self.mover, self.ce_use, self.pieces = mover, ce_use, pieces
         self._symm_mem = symm_mem
         self._symm_group = group if group is not None else dist.group.WORLD
         self._handles = {}
@@ -527,15 +692,22 @@ class FusedZero1Optimizer(ShardedAmpOptimizer):
         with torch.cuda.device(self.device):
             self.pairs = symm_mem.empty(2 * self.world, dtype=torch.float64, device=self.device)
             self.pairs.zero_()
-            self._handles["pairs"] = symm_mem.rendezvous(self.pairs, self._symm_group)
-            for name in ("grads16", "weights16"):
+            self.sync_block = symm_mem.empty(_lib.ZERO1_SYNC_BYTES // 4, dtype=torch.int32, device=self.device)
+            zero1_sync_init(self.sync_block)
+            torch.cuda.current_stream().synchronize()
+            for name in ("pairs", "sync_block", "grads16", "weights16"):
                 self._handles[name] = symm_mem.rendezvous(getattr(self, name), self._symm_group)
             shard_bytes = self.begin * 2
             self._grad_ptrs = [int(p) + shard_bytes for p in self._handles["grads16"].buffer_ptrs]
             self._weight_ptrs = [int(p) + shard_bytes for p in self._handles["weights16"].buffer_ptrs]
             self._pair_ptrs = [int(p) for p in self._handles["pairs"].buffer_ptrs]
+            self.sync = make_sync([int(p) for p in self._handles["sync_block"].buffer_ptrs], wait_limit)
+            self.staging = None
+            if mover == "ce" and "rs" in ce_use and self.world > 1:
+                self.staging = torch.empty((self.world - 1) * self.n_local, dtype=torch.float16, device=self.device)
             torch.cuda.current_stream().synchronize()
-            self._barrier("pairs")
+        # once, on the host: every rank's block is zeroed and mapped before any rank announces anything
+        dist.barrier(group=self._symm_group)
 
     def _alloc_arena16(self, name: str) -> torch.Tensor:
         with torch.cuda.device(self.device):
@@ -543,25 +715,52 @@ class FusedZero1Optimizer(ShardedAmpOptimizer):
             t.zero_()
             return t
 
-    def _barrier(self, which: str) -> None:
-        self._handles[which].barrier(channel=0, timeout_ms=self.BARRIER_TIMEOUT_MS)
-
     def fused_pass1(self) -> None:
-        rs_pass1_f16(self._grad_ptrs, self.rank, self.grad_shard, self.n_local, self.state, self.workspace,
-                     self._pair_ptrs)
-
-    def fused_pass2(self) -> None:
-        pass2_ag_f16(self.master, self.m, self.v, self.grad_shard, self._weight_ptrs, self.n_local, self.begin,
-                     self.tensors, self.ntensors, self.state, self.beta1, self.beta2, self.eps)
+        if self.mover == "ce" and "rs" in self.ce_use and self.world > 1:
+            rs_pass1_f16_ce(self._grad_ptrs, self.rank, self.staging, self.grad_shard, self.n_local, self.pieces,
+                            self.state, self.workspace, self._pair_ptrs, self.sync)
+        else:
+            rs_pass1_f16_sync(self._grad_ptrs, self.rank, self.grad_shard, self.n_local, self.state, self.workspace,
+                              self._pair_ptrs, self.sync)
 
     def finalize_pairs(self) -> None:
-        finalize_sums(self.state, self.pairs, self.world, self.sched, self.history, self.history_len)
+        finalize_sums_sync(self.state, self.pairs, self.world, self.rank, self.sched, self.sync, self.history,
+                           self.history_len)
+
+    def fused_pass2(self) -> None:
+        if self.mover == "ce" and "ag" in self.ce_use and self.world > 1:
+            pass2_ag_f16_ce(self.master, self.m, self.v, self.grad_shard, self._weight_ptrs, self.rank,
+                            self.n_local, self.begin, self.tensors, self.ntensors, self.state, self.beta1,
+                            self.beta2, self.eps, self.pieces)
+        else:
+            pass2_ag_f16(self.master, self.m, self.v, self.grad_shard, self._weight_ptrs, self.n_local, self.begin,
+                         self.tensors, self.ntensors, self.state, self.beta1, self.beta2, self.eps)
+
+    def end_step(self) -> None:
+        zero1_barrier(self.sync, self.world, self.rank, _lib.PHASE_WEIGHTS,
+                      _lib.SYNC_SIGNAL | _lib.SYNC_WAIT | _lib.SYNC_ADVANCE)
 
     def optimizer_step(self) -> None:
         with torch.cuda.device(self.device):
-            self._barrier("grads16")
             self.fused_pass1()
-            self._barrier("pairs")
             self.finalize_pairs()
             self.fused_pass2()
-            self._barrier("weights16")
+            self.end_step()
+
+    def sync_status(self) -> Tuple[int, int]:
+        """(steps the flag block has counted, error word); synchronises this rank's stream."""
+        with torch.cuda.device(self.device):
+            return zero1_sync_read(self.sync_block)
+
+    def read_state(self) -> StepState:
+        """The 60-byte state; raises RankWaitError if a kernel of this rank stopped waiting for
+        another rank (the step in flight was not applied and the ranks are out of step: restore
+        a checkpoint and build the optimizers again)."""
+        st = super().read_state()
+        _, error = self.sync_status()
+        if error != 0:
+            phase, missing = (error & 0xFF) - 1, error >> 8
+            what = self.PHASE_NAMES[phase] if 0 <= phase < 3 else f"phase {phase}"
+            raise RankWaitError(_lib.ERR_CUDA, f"rank {self.rank} gave up waiting for '{what}' of rank {missing}; "
+                                "the step was not applied")
+        return st

@@ -83,18 +83,34 @@ __device__ __forceinline__ int table_load(TensorTable &tab, const b200amp_tensor
     return base;
 }
 
-struct Cursor
-{
-    int k;              // the last tensor whose first element is <= the position (0 if none is)
-    long long next;     // first element of tensor k + 1, LLONG_MAX past the end
-    float factor;       // what a parameter of tensor k is multiplied by: the step's decay, or 1
-};
+// The same runs as a kernel PARAMETER (1 KB in the constant bank) for tables of at most
+// B200AMP_MAX_RUNS runs, built on the host by b200amp_decay_runs_build: no shared memory, no
+// loading prologue and no CTA barrier in the kernel that takes it. Offsets are multiples of 4,
+// so a run's first element is kept divided by 4 in 32 bits; merged runs alternate, so one flag
+// (of run 0) gives them all.
+using DecayRuns = b200amp_decay_runs;
 
-// Reads of the table go through volatile accesses: they belong to the rare trip that crosses a
-// run's end, and must not be hoisted by the compiler into the trip that does not.
+// ---- what the cursor needs from a table, for both forms
+__device__ __forceinline__ long long table_first(const TensorTable &tab, int k)
+{
+    return tab.first[k];
+}
+
+__device__ __forceinline__ long long table_first(const DecayRuns &tab, int k)
+{
+    return static_cast<long long>(tab.first4[k]) * 4;
+}
+
+// Reads of the shared-memory table go through volatile accesses: they belong to the rare trip
+// that crosses a run's end, and must not be hoisted by the compiler into the trip that does not.
 __device__ __forceinline__ long long table_next(const TensorTable &tab, int ntensors, int k)
 {
     return k + 1 < ntensors ? *static_cast<const volatile long long *>(&tab.first[k + 1]) : LLONG_MAX;
+}
+
+__device__ __forceinline__ long long table_next(const DecayRuns &tab, int nruns, int k)
+{
+    return k + 1 < nruns ? static_cast<long long>(tab.first4[k + 1]) * 4 : LLONG_MAX;
 }
 
 __device__ __forceinline__ float table_factor(const TensorTable &tab, int k, float wd_decay)
@@ -102,13 +118,26 @@ __device__ __forceinline__ float table_factor(const TensorTable &tab, int k, flo
     return *static_cast<const volatile unsigned char *>(&tab.decay[k]) ? wd_decay : 1.0f;
 }
 
-__device__ __forceinline__ Cursor cursor_seek(const TensorTable &tab, int ntensors, long long at, float wd_decay)
+__device__ __forceinline__ float table_factor(const DecayRuns &tab, int k, float wd_decay)
+{
+    return ((tab.flag0 ^ k) & 1) ? wd_decay : 1.0f;
+}
+
+struct Cursor
+{
+    int k;              // the last run whose first element is <= the position (0 if none is)
+    long long next;     // first element of run k + 1, LLONG_MAX past the end
+    float factor;       // what a parameter of run k is multiplied by: the step's decay, or 1
+};
+
+template <class Table>
+__device__ __forceinline__ Cursor cursor_seek(const Table &tab, int ntensors, long long at, float wd_decay)
 {
     int lo = 0, hi = ntensors - 1;
     while (lo < hi)
     {
         const int mid = (lo + hi + 1) >> 1;
-        if (tab.first[mid] <= at)
+        if (table_first(tab, mid) <= at)
         {
             lo = mid;
         }
@@ -124,9 +153,10 @@ __device__ __forceinline__ Cursor cursor_seek(const TensorTable &tab, int ntenso
     return c;
 }
 
-// Positions only grow. Nothing to do (one compare, no shared-memory access) while the
-// position stays inside tensor k, which is the case for all but a few hundred trips.
-__device__ __forceinline__ void cursor_advance(Cursor &c, const TensorTable &tab, int ntensors, long long at,
+// Positions only grow. Nothing to do (one compare, no table access) while the position stays
+// inside run k, which is the case for all but a few hundred trips.
+template <class Table>
+__device__ __forceinline__ void cursor_advance(Cursor &c, const Table &tab, int ntensors, long long at,
                                                float wd_decay)
 {
     if (at >= c.next)
@@ -142,8 +172,9 @@ __device__ __forceinline__ void cursor_advance(Cursor &c, const TensorTable &tab
 
 // Decay factors of the two quads of the 8-element group that starts at `at`. Tensor
 // offsets are multiples of 4, so a quad never straddles two tensors but a group can.
-// The usual case, the whole group inside the cursor's tensor, costs one compare.
-__device__ __forceinline__ void group_decay(Cursor &c, const TensorTable &tab, int ntensors, long long at,
+// The usual case, the whole group inside the cursor's run, costs one compare.
+template <class Table>
+__device__ __forceinline__ void group_decay(Cursor &c, const Table &tab, int ntensors, long long at,
                                             float wd_decay, float &lo, float &hi)
 {
     if (at + 8 <= c.next)

@@ -20,6 +20,7 @@ void set_error(const char *fmt, ...);           // text for b200amp_last_error()
 int cuda_fail(cudaError_t err, const char *what, const char *file, int line);
 void count_launch();                            // one more kernel launch enqueued
 int sm_count();                                 // SMs of the current device (cached per device), <= 0 on error
+int zero1_sync_timeout_take(int *out);          // zero1.cu: *out = 1 if a wait on another rank gave up (clears it)
 
 struct Tunables
 {
@@ -33,6 +34,8 @@ struct Tunables
     int rs_blocks_per_sm;       // resident CTAs per SM of the fused reduce-scatter + pass 1
     int ag_blocks_per_sm;       // resident CTAs per SM of the fused pass 2 + all-gather, 0 = by rank count
     int bridge_blocks_per_sm;   // CTAs per SM asked for by the fp32 -> fp16 bridge (cast + pass 1)
+    int pass2_carveout;         // -1, or the shared-memory carve-out (percent) asked for pass 2's registers-only kernel
+    int ce_lanes;               // copy streams the copy-engine forms of the ZeRO-1 step spread their copies over
 };
 Tunables &tunables();
 

@@ -79,6 +79,47 @@ __global__ void __launch_bounds__(THREADS)
     }
 }
 
+// The same sweep with the decay runs as a kernel parameter (b200amp_decay_runs, at most
+// B200AMP_MAX_RUNS of them: a GPT layout has 8 per layer + 3). No static shared memory, no table
+// prologue, no CTA barrier: a CTA starts loading with its first instruction.
+template <int THREADS, int ST>
+__global__ void __launch_bounds__(THREADS)
+    pass2_f16_runs_kernel(float *__restrict__ master, float *__restrict__ m, float *__restrict__ v,
+                          const uint4 *__restrict__ g16, uint4 *__restrict__ w16, long long n8,
+                          long long arena_offset, const __grid_constant__ DecayRuns runs,
+                          const b200amp_step_state *__restrict__ st, float b1, float b2, float eps)
+{
+    if (st->found_inf)
+    {
+        return;
+    }
+    const float wd_decay = st->decay;
+    const StepFactors f = step_factors(st, b1, b2, eps);
+    const int nruns = runs.nruns;
+    const int groups = static_cast<int>(n8);
+    const int stride = static_cast<int>(gridDim.x) * THREADS;
+    int i = static_cast<int>(blockIdx.x) * THREADS + static_cast<int>(threadIdx.x);
+    if (i >= groups)
+    {
+        return;
+    }
+    Cursor cur = cursor_seek(runs, nruns, arena_offset + static_cast<long long>(i) * 8, wd_decay);
+    for (; i < groups; i += stride)
+    {
+        const long long at = arena_offset + static_cast<long long>(i) * 8;
+        update_group<ST>(
+            master, m, v, g16, i,
+            [&](float &d_lo, float &d_hi) { group_decay(cur, runs, nruns, at, wd_decay, d_lo, d_hi); },
+            [&](int j, const uint4 &half8) {
+                if (w16 != nullptr)
+                {
+                    store_h8<ST>(w16 + j, half8);
+                }
+            },
+            f);
+    }
+}
+
 // ---------------------------------------------------------------- shared-memory staged kernel
 
 constexpr int BULK_TILE = 2048;                 // elements per tile
@@ -362,6 +403,16 @@ static void launch_registers(int st_hint, int grid, cudaStream_t s, float *maste
                              const b200amp_tensor_info *tensors, int ntensors, const b200amp_step_state *st, float b1,
                              float b2, float eps)
 {
+    // measurement knob: the L1 / shared-memory split asked for (percent of shared memory), applied
+    // when it changes; -1 leaves the driver's choice
+    static int applied_carveout = -1;
+    const int carveout = tunables().pass2_carveout;
+    if (carveout != applied_carveout)
+    {
+        cudaFuncSetAttribute(pass2_f16_kernel<THREADS, 1>, cudaFuncAttributePreferredSharedMemoryCarveout, carveout);
+        cudaFuncSetAttribute(pass2_f16_kernel<THREADS, 0>, cudaFuncAttributePreferredSharedMemoryCarveout, carveout);
+        applied_carveout = carveout;
+    }
     if (st_hint == 1)
     {
         pass2_f16_kernel<THREADS, 1><<<grid, THREADS, 0, s>>>(master, m, v, g16, w16, n8, arena_offset, tensors,
@@ -486,8 +537,104 @@ extern "C" B200AMP_API int b200amp_pass2_f16(float *master, float *m, float *v, 
     return B200AMP_OK;
 }
 
-// 1 if a shared-memory staged launch on the current device gave up waiting for a copy since the
-// last call (the flag is cleared by reading it). Synchronises the device.
+// The tensor table as runs of equal decay flag, for b200amp_pass2_f16_runs. Host only.
+extern "C" B200AMP_API int b200amp_decay_runs_build(const b200amp_tensor_info *host_table, int ntensors,
+                                                    b200amp_decay_runs *out)
+{
+    B200AMP_REQUIRE(out != nullptr, "decay_runs_build: out is null");
+    int rc = b200amp_check_tensor_table(host_table, ntensors, 0);
+    if (rc != B200AMP_OK)
+    {
+        return rc;
+    }
+    b200amp_decay_runs runs = {};
+    for (int k = 0; k < ntensors; k++)
+    {
+        const int flag = host_table[k].decay ? 1 : 0;
+        if (k > 0 && (host_table[k - 1].decay ? 1 : 0) == flag)
+        {
+            continue;
+        }
+        if (runs.nruns == B200AMP_MAX_RUNS)
+        {
+            set_error("decay_runs_build: more than %d runs of equal decay flag; use b200amp_pass2_f16 with the "
+                      "table in device memory",
+                      B200AMP_MAX_RUNS);
+            return B200AMP_ERR_LIMIT;
+        }
+        if (host_table[k].offset / 4 > 0xFFFFFFFFLL)
+        {
+            set_error("decay_runs_build: entry %d starts at %lld, beyond the 17,179,869,180 elements a run can "
+                      "start at",
+                      k, host_table[k].offset);
+            return B200AMP_ERR_LIMIT;
+        }
+        if (runs.nruns == 0)
+        {
+            runs.flag0 = flag;
+        }
+        runs.first4[runs.nruns++] = static_cast<unsigned int>(host_table[k].offset / 4);
+    }
+    *out = runs;
+    return B200AMP_OK;
+}
+
+extern "C" B200AMP_API int b200amp_pass2_f16_runs(float *master, float *m, float *v, const void *grads16,
+                                                  void *weights16, long long n, long long arena_offset,
+                                                  const b200amp_decay_runs *runs, const b200amp_step_state *st,
+                                                  float beta1, float beta2, float eps, b200amp_stream s)
+{
+    B200AMP_REQUIRE(master != nullptr && m != nullptr && v != nullptr && grads16 != nullptr && st != nullptr &&
+                        runs != nullptr,
+                    "pass 2 (runs): null pointer");
+    B200AMP_REQUIRE(n > 0 && n % 8 == 0, "pass 2 (runs): n = %lld must be a positive multiple of 8", n);
+    if (n / 8 > (1LL << 31) - (1LL << 23))
+    {
+        set_error("pass 2 (runs): n = %lld is beyond the 17,112,760,320 elements one launch addresses; split the "
+                  "range",
+                  n);
+        return B200AMP_ERR_LIMIT;
+    }
+    B200AMP_REQUIRE(arena_offset >= 0 && arena_offset % 4 == 0,
+                    "pass 2 (runs): arena_offset = %lld must be a multiple of 4", arena_offset);
+    B200AMP_REQUIRE(aligned(master, 32) && aligned(m, 32) && aligned(v, 32),
+                    "pass 2 (runs): master, m and v must be 32-byte aligned");
+    B200AMP_REQUIRE(aligned(grads16, 16) && aligned(weights16, 16),
+                    "pass 2 (runs): the fp16 arenas must be 16-byte aligned");
+    B200AMP_REQUIRE(runs->nruns > 0 && runs->nruns <= B200AMP_MAX_RUNS, "pass 2 (runs): nruns = %d, must be in 1..%d",
+                    runs->nruns, B200AMP_MAX_RUNS);
+    const int sms = sm_count();
+    if (sms <= 0)
+    {
+        return B200AMP_ERR_CUDA;
+    }
+    const Tunables &t = tunables();
+    const long long n8 = n / 8;
+    long long want = (n8 + 255) / 256;
+    int grid = sms * t.pass2_blocks_per_sm;
+    if (grid > want)
+    {
+        grid = static_cast<int>(want);
+    }
+    const uint4 *g16 = static_cast<const uint4 *>(grads16);
+    uint4 *w16 = static_cast<uint4 *>(weights16);
+    if (t.pass2_store_hint == 1)
+    {
+        pass2_f16_runs_kernel<256, 1><<<grid, 256, 0, as_stream(s)>>>(master, m, v, g16, w16, n8, arena_offset, *runs,
+                                                                      st, beta1, beta2, eps);
+    }
+    else
+    {
+        pass2_f16_runs_kernel<256, 0><<<grid, 256, 0, as_stream(s)>>>(master, m, v, g16, w16, n8, arena_offset, *runs,
+                                                                      st, beta1, beta2, eps);
+    }
+    B200AMP_LAUNCHED();
+    return B200AMP_OK;
+}
+
+// What gave up a bounded wait on the current device since the last call, as a bit mask (the flags
+// are cleared by reading them): 1 = a shared-memory staged launch waiting for a bulk copy,
+// 2 = a ZeRO-1 kernel waiting for another rank. Synchronises the device.
 extern "C" B200AMP_API int b200amp_device_error(int *out)
 {
     B200AMP_REQUIRE(out != nullptr, "device_error: out is null");
@@ -498,6 +645,12 @@ extern "C" B200AMP_API int b200amp_device_error(int *out)
         const int zero = 0;
         B200AMP_CUDA(cudaMemcpyToSymbol(g_bulk_timeout, &zero, sizeof(int)));
     }
-    *out = flag;
+    int rank_wait = 0;
+    int rc = zero1_sync_timeout_take(&rank_wait);
+    if (rc != B200AMP_OK)
+    {
+        return rc;
+    }
+    *out = (flag != 0 ? 1 : 0) | (rank_wait != 0 ? 2 : 0);
     return B200AMP_OK;
 }

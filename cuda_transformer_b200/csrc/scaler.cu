@@ -17,94 +17,11 @@
 #include <cmath>
 #include <mutex>
 
+#include "finalize.cuh"
 #include "pass1_common.cuh"
 
 namespace b200amp
 {
-
-// ---------------------------------------------------------------- finalize (shared)
-
-// Learning rate of a 0-based step: linear warmup, then cosine to min_lr, or (decay_steps > 0)
-// flat then 1 - sqrt down over the last decay_steps. Double throughout, the numbers of
-// cuda/kernels/scaler.cu:69-93 and reference/train.py:79-96.
-__device__ double schedule_lr(int step, const b200amp_schedule &c)
-{
-    const double peak = static_cast<double>(c.lr);
-    const double floor_lr = static_cast<double>(c.min_lr);
-    if (step < c.warmup_steps)
-    {
-        return peak * (step + 1) / c.warmup_steps;
-    }
-    if (step >= c.max_steps)
-    {
-        return floor_lr;
-    }
-    if (c.decay_steps > 0)
-    {
-        const int knee = c.max_steps - c.decay_steps;
-        if (step < knee)
-        {
-            return peak;
-        }
-        const double frac = static_cast<double>(step - knee) / c.decay_steps;
-        return floor_lr + (peak - floor_lr) * (1.0 - sqrt(frac));
-    }
-    const int span = c.max_steps - c.warmup_steps;
-    const double frac = static_cast<double>(step - c.warmup_steps) / (span > 1 ? span : 1);
-    return floor_lr + 0.5 * (1.0 + cos(3.14159265358979323846 * frac)) * (peak - floor_lr);
-}
-
-// One thread. sumsq is the squared norm of the unscaled gradients, bad the inf/NaN
-// flag. Field by field what cuda/kernels/scaler.cu:131-170 does: a skipped step
-// halves S and leaves adam_t alone; a finite one advances adam_t, computes the bias
-// corrections in double from the float betas, and doubles S after growth_interval
-// finite steps in a row.
-__device__ void finalize_state(b200amp_step_state *st, double sumsq, int bad, const b200amp_schedule &c,
-                               b200amp_step_state *history, int history_len, bool set_begin_fields)
-{
-    b200amp_step_state s = *st;
-    if (set_begin_fields)
-    {
-        s.inv_scale = 1.0f / s.loss_scale;      // of THIS step: S changes below, the unscale factor must not
-        s.found_inf = bad;
-    }
-    const float norm = static_cast<float>(sqrt(sumsq));
-    s.grad_norm = norm;
-    s.clip_coef = fminf(1.0f, c.grad_clip / (norm + 1e-6f));
-    const double lr = schedule_lr(s.step, c);
-    s.lr = static_cast<float>(lr);
-    if (s.found_inf)
-    {
-        s.skipped += 1;
-        s.good_steps = 0;
-        if (c.dynamic_scale)
-        {
-            s.loss_scale *= 0.5f;
-        }
-    }
-    else
-    {
-        s.adam_t += 1;
-        const double t = static_cast<double>(s.adam_t);
-        const double bc1 = 1.0 - pow(static_cast<double>(c.beta1), t);
-        const double bc2 = 1.0 - pow(static_cast<double>(c.beta2), t);
-        s.step_size = static_cast<float>(lr / bc1);
-        s.bc2_sqrt = static_cast<float>(sqrt(bc2));
-        s.decay = static_cast<float>(1.0 - lr * c.weight_decay);
-        s.good_steps += 1;
-        if (c.dynamic_scale && s.good_steps >= c.growth_interval)
-        {
-            s.loss_scale *= 2.0f;
-            s.good_steps = 0;
-        }
-    }
-    if (history != nullptr)
-    {
-        history[s.step % history_len] = s;
-    }
-    s.step += 1;
-    *st = s;
-}
 
 // ---------------------------------------------------------------- compat kernels
 
@@ -480,6 +397,8 @@ extern "C" B200AMP_API int b200amp_finalize_sums(b200amp_step_state *st, const d
 namespace b200amp
 {
 
+// A limit of this entry point by policy, not one the array imposes: the 4,736 partial sums cover
+// any n (the virtual blocks just grow), but a stated maximum is part of this entry point's contract.
 constexpr long long STATIC_PASS1_MAX_ELEMENTS = 1LL << 32;     // 4,294,967,296 fp16 gradients (8 GiB)
 
 static __device__ __align__(256) unsigned char g_pass1_scratch[sizeof(Workspace)];
@@ -515,8 +434,13 @@ static int pass1_scratch_address(Workspace **out)
 extern "C" B200AMP_API int b200amp_pass1_f16_static(const void *grads16, long long n, const b200amp_step_state *st,
                                                     double *sums_out, b200amp_stream s)
 {
+    // every argument is checked before anything is enqueued: a refused call leaves the shared
+    // array and the stream untouched
     B200AMP_REQUIRE(sums_out != nullptr, "pass1_f16_static: sums_out is null");
     B200AMP_REQUIRE(aligned(sums_out, 8), "pass1_f16_static: sums_out must be 8-byte aligned");
+    B200AMP_REQUIRE(grads16 != nullptr && st != nullptr, "pass1_f16_static: null pointer");
+    B200AMP_REQUIRE(aligned(grads16, 16), "pass1_f16_static: the fp16 gradient pointer must be 16-byte aligned");
+    B200AMP_REQUIRE(n > 0 && n % 8 == 0, "pass1_f16_static: n = %lld must be a positive multiple of 8", n);
     if (n > STATIC_PASS1_MAX_ELEMENTS)
     {
         set_error("pass1_f16_static: n = %lld is beyond the %lld elements this entry point accepts; "

@@ -13,19 +13,24 @@
 //                          stored into every rank's weight arena (plain 128-bit peer stores)
 //                          as they are produced.
 //
-// Neither kernel waits on another GPU: ordering between ranks (gradients ready before they are
-// pulled, pair tables complete before the finalize, weight arenas complete before the next
-// forward pass) is the caller's, with stream-ordered barriers between the launches. No
-// multicast loads, no TMA from peer memory: every remote access is an ordinary ld/st.global.
-// The reference has no multi-GPU code; the arithmetic per element is that of pass 1 / pass 2.
+// Ordering between ranks (gradients ready before they are pulled, pair tables complete before
+// the finalize, weight arenas complete before the next forward pass) is either the caller's
+// (events between the ranks' streams in a one-process host) or the library's own: the ..._sync
+// entry points exchange step numbers through a small block of flag words per rank
+// (zero1_sync.cuh), every wait bounded, a give-up reported instead of a hang. No multicast
+// loads, no TMA from peer memory: every remote access is an ordinary ld/st.global or a
+// cudaMemcpyAsync. The reference has no multi-GPU code; the arithmetic per element is that of
+// pass 1 / pass 2.
+
+#include <mutex>
 
 #include "adamw_math.cuh"
+#include "finalize.cuh"
 #include "pass1_common.cuh"
+#include "zero1_sync.cuh"
 
 namespace b200amp
 {
-
-constexpr int MAX_RANKS = 8;
 
 struct ConstPtrs
 {
@@ -80,20 +85,41 @@ constexpr int RS_UNROLL = B200AMP_RS_UNROLL;    // vectors per thread per trip: 
 
 // src.p[r]: the start of THIS rank's slice inside rank r's gradient arena. reduced: local.
 // pair_tables.p[r]: rank r's table of R pairs {sum, flag}; this rank fills entry my_rank of each.
+// This launch owns the virtual blocks vb_first .. vb_first + vb_count - 1 of the slice's fixed
+// partition (all of them when the slice is reduced in one launch). A launch with last_part == 0
+// leaves its partial sums and its flag in the workspace for the launch that ends the slice (same
+// stream, so they are complete before that one starts).
+// sy: the ranks' flag blocks (off when block[0] is null). SYNC_ENTER_GRADS: every CTA announces
+// this rank's gradients and waits for every rank's before it loads anything; a CTA whose wait
+// gave up does no work. SYNC_SIGNAL_PAIRS: the last CTA announces the pairs it has written.
 template <int R>
 __global__ void __launch_bounds__(P1_THREADS)
     rs_pass1_f16_kernel(ConstPtrs src, uint4 *__restrict__ reduced, long long n8, const b200amp_step_state *st,
-                        Workspace *ws, Ptrs pair_tables, int my_rank)
+                        Workspace *ws, Ptrs pair_tables, int my_rank, int vb_first, int vb_count, int last_part,
+                        SyncArgs sy)
 {
     __shared__ double warp_part[P1_WARPS];
     __shared__ int last_block;
+
+    bool alive = true;
+    if (sync_on(sy))
+    {
+        bool ok = true;
+        if (threadIdx.x < R)
+        {
+            ok = (sy.mode & SYNC_ENTER_GRADS) ? sync_exchange(sy, SYNC_PHASE_GRADS, threadIdx.x, true, true)
+                                               : !sync_failed(sy);
+        }
+        alive = __syncthreads_and(ok) != 0;
+    }
 
     const float inv = 1.0f / st->loss_scale;
     const float inv_ranks = 1.0f / static_cast<float>(R);      // exact: R is a power of two
     const P1Partition part = p1_partition(n8);
     uint32_t bad = 0;
 
-    for (int vb = blockIdx.x; vb < part.vblocks; vb += gridDim.x)
+    const int vb_end = alive ? vb_first + vb_count : 0;         // a CTA that gave up walks no blocks
+    for (int vb = vb_first + blockIdx.x; vb < vb_end; vb += gridDim.x)
     {
         const long long begin = static_cast<long long>(vb) * part.vec_per_vblock;
         long long end = begin + part.vec_per_vblock;
@@ -145,6 +171,16 @@ __global__ void __launch_bounds__(P1_THREADS)
         vblock_store_partial(mine, warp_part, ws, vb);
     }
 
+    if (!last_part)
+    {
+        const int block_bad = __syncthreads_or(bad != 0);
+        if (threadIdx.x == 0 && block_bad)
+        {
+            atomicOr(&ws->bad, 1);
+        }
+        return;
+    }
+    // the ticket is taken even after a give-up, so the workspace is re-armed for the next launch
     if (!pass1_take_ticket(bad, ws, &last_block))
     {
         return;
@@ -154,6 +190,10 @@ __global__ void __launch_bounds__(P1_THREADS)
     const double total = pass1_final_sum(part, ws, tree, &any_bad);
     if (threadIdx.x == 0)
     {
+        if (sync_on(sy) && sync_failed(sy))
+        {
+            return;                             // some CTA gave up: no pair, no announcement
+        }
 #pragma unroll
         for (int r = 0; r < R; r++)
         {
@@ -165,6 +205,67 @@ __global__ void __launch_bounds__(P1_THREADS)
             }
         }
         __threadfence_system();                 // the pairs reach the peers before this grid is seen as done
+        if (sync_on(sy) && (sy.mode & SYNC_SIGNAL_PAIRS))
+        {
+            const unsigned int e = sync_epoch(sy);
+#pragma unroll
+            for (int r = 0; r < R; r++)
+            {
+                sync_signal(sy, SYNC_PHASE_PAIRS, r, e);
+            }
+        }
+    }
+}
+
+// The finalize of the sharded step with its own wait: thread q waits for rank q's "pairs written"
+// of the step in flight, then thread 0 adds the pairs in rank order (identical bits on every
+// rank) and runs the finalize. When a wait here or earlier in the step gave up, the state is left
+// as it is except found_inf = 1, so the pass 2 that follows on the stream changes nothing.
+__global__ void finalize_sums_sync_kernel(b200amp_step_state *st, const double *sums, int nranks,
+                                          b200amp_schedule cfg, b200amp_step_state *history, int history_len,
+                                          SyncArgs sy)
+{
+    bool ok = true;
+    if (static_cast<int>(threadIdx.x) < nranks)
+    {
+        ok = sync_exchange(sy, SYNC_PHASE_PAIRS, threadIdx.x, false, true);
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (threadIdx.x != 0)
+    {
+        return;
+    }
+    if (!ok)
+    {
+        st->found_inf = 1;
+        return;
+    }
+    const volatile double *pairs = sums;        // written by the peers: read from memory, not a cache line of before
+    double total = 0.0;
+    int bad = 0;
+    for (int r = 0; r < nranks; r++)
+    {
+        total += pairs[2 * r];
+        bad |= (pairs[2 * r + 1] != 0.0) ? 1 : 0;
+    }
+    finalize_state(st, total, bad, cfg, history, history_len, true);
+}
+
+// One warp. what & 1: announce `phase` of the step in flight to every rank; & 2: wait for it from
+// every rank; & 4: the step is over on this rank, advance its counter (only if nothing gave up).
+__global__ void zero1_barrier_kernel(SyncArgs sy, int nranks, int phase, int what)
+{
+    bool ok = true;
+    unsigned int e = 0;
+    if (static_cast<int>(threadIdx.x) < nranks)
+    {
+        e = sync_epoch(sy);
+        ok = sync_exchange(sy, phase, threadIdx.x, (what & 1) != 0, (what & 2) != 0);
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (threadIdx.x == 0 && ok && (what & 4))
+    {
+        sync_local(sy)[SYNC_EPOCH] = e;
     }
 }
 
@@ -225,10 +326,32 @@ static int check_ranks(int nranks, int my_rank, const char *who)
 
 using namespace b200amp;
 
-extern "C" B200AMP_API int b200amp_rs_pass1_f16(const void *const *grads16_by_rank, int nranks, int my_rank,
-                                                void *reduced16, long long n, const b200amp_step_state *st,
-                                                void *workspace, double *const *pair_table_by_rank,
-                                                b200amp_stream s)
+// The flag blocks of a b200amp_zero1_sync as kernel arguments. sync == null: off.
+static int sync_args(const b200amp_zero1_sync *sync, int nranks, int my_rank, int mode, const char *who,
+                     SyncArgs *out)
+{
+    SyncArgs a = {};
+    a.my_rank = my_rank;
+    a.mode = mode;
+    if (sync != nullptr)
+    {
+        for (int r = 0; r < nranks; r++)
+        {
+            B200AMP_REQUIRE(sync->block_by_rank[r] != nullptr && aligned(sync->block_by_rank[r], 16),
+                            "%s: flag block of rank %d is null or not 16-byte aligned", who, r);
+            a.block[r] = static_cast<unsigned int *>(sync->block_by_rank[r]);
+        }
+        a.limit = sync->wait_limit;
+    }
+    *out = a;
+    return B200AMP_OK;
+}
+
+// vblock_count < 0: the whole slice in one launch.
+static int rs_pass1_launch(const void *const *grads16_by_rank, int nranks, int my_rank, void *reduced16, long long n,
+                           int vblock_first, int vblock_count, int last_part, const b200amp_step_state *st,
+                           void *workspace, double *const *pair_table_by_rank, const b200amp_zero1_sync *sync,
+                           int sync_mode, b200amp_stream s)
 {
     int rc = check_ranks(nranks, my_rank, "rs_pass1");
     if (rc != B200AMP_OK)
@@ -250,6 +373,12 @@ extern "C" B200AMP_API int b200amp_rs_pass1_f16(const void *const *grads16_by_ra
         tables.p[r] = pair_table_by_rank != nullptr ? pair_table_by_rank[r] : nullptr;
         B200AMP_REQUIRE(aligned(tables.p[r], 8), "rs_pass1: pair table of rank %d is not 8-byte aligned", r);
     }
+    SyncArgs sy;
+    rc = sync_args(sync, nranks, my_rank, sync_mode, "rs_pass1", &sy);
+    if (rc != B200AMP_OK)
+    {
+        return rc;
+    }
     const int sms = sm_count();
     if (sms <= 0)
     {
@@ -257,23 +386,165 @@ extern "C" B200AMP_API int b200amp_rs_pass1_f16(const void *const *grads16_by_ra
     }
     const long long n8 = n / 8;
     const P1Partition part = p1_partition(n8);
-    int grid = sms * tunables().rs_blocks_per_sm;
-    if (grid > part.vblocks)
+    if (vblock_count < 0)
     {
-        grid = part.vblocks;
+        vblock_first = 0;
+        vblock_count = part.vblocks;
+        last_part = 1;
+    }
+    B200AMP_REQUIRE(vblock_first >= 0 && vblock_count > 0 && vblock_first + vblock_count <= part.vblocks,
+                    "rs_pass1: virtual blocks %d .. %d are not inside the slice's %d", vblock_first,
+                    vblock_first + vblock_count - 1, part.vblocks);
+    int grid = sms * tunables().rs_blocks_per_sm;
+    if (grid > vblock_count)
+    {
+        grid = vblock_count;
     }
     uint4 *out = static_cast<uint4 *>(reduced16);
     Workspace *ws = static_cast<Workspace *>(workspace);
     cudaStream_t stream = as_stream(s);
+    const int fin = last_part ? 1 : 0;
+#define B200AMP_RS(R)                                                                                            \
+    rs_pass1_f16_kernel<R><<<grid, P1_THREADS, 0, stream>>>(src, out, n8, st, ws, tables, my_rank, vblock_first, \
+                                                            vblock_count, fin, sy)
     switch (nranks)
     {
-    case 1: rs_pass1_f16_kernel<1><<<grid, P1_THREADS, 0, stream>>>(src, out, n8, st, ws, tables, my_rank); break;
-    case 2: rs_pass1_f16_kernel<2><<<grid, P1_THREADS, 0, stream>>>(src, out, n8, st, ws, tables, my_rank); break;
-    case 4: rs_pass1_f16_kernel<4><<<grid, P1_THREADS, 0, stream>>>(src, out, n8, st, ws, tables, my_rank); break;
-    default: rs_pass1_f16_kernel<8><<<grid, P1_THREADS, 0, stream>>>(src, out, n8, st, ws, tables, my_rank); break;
+    case 1: B200AMP_RS(1); break;
+    case 2: B200AMP_RS(2); break;
+    case 4: B200AMP_RS(4); break;
+    default: B200AMP_RS(8); break;
     }
+#undef B200AMP_RS
     B200AMP_LAUNCHED();
     return B200AMP_OK;
+}
+
+extern "C" B200AMP_API int b200amp_rs_pass1_f16(const void *const *grads16_by_rank, int nranks, int my_rank,
+                                                void *reduced16, long long n, const b200amp_step_state *st,
+                                                void *workspace, double *const *pair_table_by_rank,
+                                                b200amp_stream s)
+{
+    return rs_pass1_launch(grads16_by_rank, nranks, my_rank, reduced16, n, 0, -1, 1, st, workspace,
+                           pair_table_by_rank, nullptr, 0, s);
+}
+
+extern "C" B200AMP_API int b200amp_rs_pass1_f16_sync(const void *const *grads16_by_rank, int nranks, int my_rank,
+                                                     void *reduced16, long long n, const b200amp_step_state *st,
+                                                     void *workspace, double *const *pair_table_by_rank,
+                                                     const b200amp_zero1_sync *sync, b200amp_stream s)
+{
+    B200AMP_REQUIRE(sync != nullptr && pair_table_by_rank != nullptr, "rs_pass1_sync: null sync or pair tables");
+    return rs_pass1_launch(grads16_by_rank, nranks, my_rank, reduced16, n, 0, -1, 1, st, workspace,
+                           pair_table_by_rank, sync, SYNC_ENTER_GRADS | SYNC_SIGNAL_PAIRS, s);
+}
+
+extern "C" B200AMP_API int b200amp_rs_pass1_f16_part(const void *const *grads16_by_rank, int nranks, int my_rank,
+                                                     void *reduced16, long long n, int vblock_first,
+                                                     int vblock_count, int last_part, const b200amp_step_state *st,
+                                                     void *workspace, double *const *pair_table_by_rank,
+                                                     b200amp_stream s)
+{
+    B200AMP_REQUIRE(vblock_count > 0, "rs_pass1 part: vblock_count = %d must be positive", vblock_count);
+    return rs_pass1_launch(grads16_by_rank, nranks, my_rank, reduced16, n, vblock_first, vblock_count, last_part, st,
+                           workspace, pair_table_by_rank, nullptr, 0, s);
+}
+
+extern "C" B200AMP_API int b200amp_pass1_partition(long long n, int *vblocks, long long *elements_per_vblock)
+{
+    B200AMP_REQUIRE(n > 0 && n % 8 == 0, "pass1_partition: n = %lld must be a positive multiple of 8", n);
+    B200AMP_REQUIRE(vblocks != nullptr && elements_per_vblock != nullptr, "pass1_partition: null output pointer");
+    const P1Partition part = p1_partition(n / 8);
+    *vblocks = part.vblocks;
+    *elements_per_vblock = part.vec_per_vblock * 8;
+    return B200AMP_OK;
+}
+
+extern "C" B200AMP_API int b200amp_copy_async(void *dst, const void *src, long long bytes, b200amp_stream s)
+{
+    B200AMP_REQUIRE(dst != nullptr && src != nullptr && bytes > 0, "copy_async: null pointer or bytes = %lld", bytes);
+    B200AMP_CUDA(cudaMemcpyAsync(dst, src, static_cast<size_t>(bytes), cudaMemcpyDefault, as_stream(s)));
+    return B200AMP_OK;
+}
+
+// ---------------------------------------------------------------- the ranks' flag blocks
+
+extern "C" B200AMP_API int b200amp_zero1_sync_init(void *block, b200amp_stream s)
+{
+    B200AMP_REQUIRE(block != nullptr && aligned(block, 16), "zero1_sync_init: block is null or not 16-byte aligned");
+    B200AMP_CUDA(cudaMemsetAsync(block, 0, B200AMP_ZERO1_SYNC_BYTES, as_stream(s)));
+    return B200AMP_OK;
+}
+
+extern "C" B200AMP_API int b200amp_zero1_sync_read(const void *block, unsigned int *steps_done,
+                                                   unsigned int *error)
+{
+    B200AMP_REQUIRE(block != nullptr, "zero1_sync_read: block is null");
+    unsigned int words[2] = {0, 0};
+    B200AMP_CUDA(cudaMemcpy(words, static_cast<const unsigned int *>(block) + SYNC_EPOCH, sizeof(words),
+                            cudaMemcpyDeviceToHost));
+    if (steps_done != nullptr)
+    {
+        *steps_done = words[0];
+    }
+    if (error != nullptr)
+    {
+        *error = words[1];
+    }
+    return B200AMP_OK;
+}
+
+extern "C" B200AMP_API int b200amp_zero1_barrier(const b200amp_zero1_sync *sync, int nranks, int my_rank, int phase,
+                                                 int what, b200amp_stream s)
+{
+    int rc = check_ranks(nranks, my_rank, "zero1_barrier");
+    if (rc != B200AMP_OK)
+    {
+        return rc;
+    }
+    B200AMP_REQUIRE(sync != nullptr, "zero1_barrier: sync is null");
+    B200AMP_REQUIRE(phase >= 0 && phase <= SYNC_PHASE_WEIGHTS, "zero1_barrier: phase = %d, must be 0, 1 or 2", phase);
+    B200AMP_REQUIRE(what > 0 && what < 8, "zero1_barrier: what = %d, must be a combination of SIGNAL, WAIT and "
+                                          "ADVANCE", what);
+    SyncArgs sy;
+    rc = sync_args(sync, nranks, my_rank, 0, "zero1_barrier", &sy);
+    if (rc != B200AMP_OK)
+    {
+        return rc;
+    }
+    zero1_barrier_kernel<<<1, 32, 0, as_stream(s)>>>(sy, nranks, phase, what);
+    B200AMP_LAUNCHED();
+    return B200AMP_OK;
+}
+
+extern "C" B200AMP_API int b200amp_finalize_sums_sync(b200amp_step_state *st, const double *sums, int nranks,
+                                                      int my_rank, const b200amp_schedule *cfg,
+                                                      b200amp_step_state *history, int history_len,
+                                                      const b200amp_zero1_sync *sync, b200amp_stream s)
+{
+    int rc = check_ranks(nranks, my_rank, "finalize_sums_sync");
+    if (rc != B200AMP_OK)
+    {
+        return rc;
+    }
+    B200AMP_REQUIRE(st != nullptr && sums != nullptr && sync != nullptr && cfg != nullptr,
+                    "finalize_sums_sync: null pointer");
+    B200AMP_REQUIRE(history == nullptr || history_len > 0, "history given with history_len %d", history_len);
+    SyncArgs sy;
+    rc = sync_args(sync, nranks, my_rank, 0, "finalize_sums_sync", &sy);
+    if (rc != B200AMP_OK)
+    {
+        return rc;
+    }
+    finalize_sums_sync_kernel<<<1, 32, 0, as_stream(s)>>>(st, sums, nranks, *cfg, history, history_len, sy);
+    B200AMP_LAUNCHED();
+    return B200AMP_OK;
+}
+
+// 1 if a wait on another rank gave up on the current device since the last call (pass2.cu's
+// b200amp_device_error reports it together with its own flag).
+int b200amp::zero1_sync_timeout_take(int *out)
+{
+    return sync_timeout_take(out);
 }
 
 extern "C" B200AMP_API int b200amp_pass2_ag_f16(float *master, float *m, float *v, const void *reduced16,
@@ -343,5 +614,244 @@ extern "C" B200AMP_API int b200amp_pass2_ag_f16(float *master, float *m, float *
     }
 #undef B200AMP_AG
     B200AMP_LAUNCHED();
+    return B200AMP_OK;
+}
+
+// ---------------------------------------------------------------- copy-engine forms
+//
+// The same two steps with the NVLink bytes moved by the copy engines instead of by loads and
+// stores that SMs issue. Measured between two B200s with both directions of the links busy: copy
+// engines 771-776 GB/s per direction, SM loads 664, SM stores 704. The slice is cut into pieces.
+// Reduce-scatter: the peers' pieces are pulled into a local staging buffer on copy streams while
+// the kernel, which then reads local memory only, reduces the piece before. All-gather: each
+// piece of fp16 weights is pushed to the peers while pass 2 works on the next. Same arithmetic,
+// same order of additions, same partition of the norm: bit-identical to the fused kernels.
+
+namespace b200amp
+{
+
+constexpr int MAX_LANES = 7;                    // one copy stream per peer at most
+constexpr int MAX_PIECES = 64;
+constexpr int MAX_DEVICES = 64;
+
+// Per device: the copy streams and a pool of events, created on first use and kept.
+struct CopyLanes
+{
+    bool ready = false;
+    cudaStream_t stream[MAX_LANES] = {};
+    cudaEvent_t start = nullptr;
+    cudaEvent_t done[MAX_LANES] = {};
+    cudaEvent_t piece[MAX_PIECES][MAX_LANES] = {};
+};
+
+static int copy_lanes(CopyLanes **out)
+{
+    static CopyLanes lanes[MAX_DEVICES];
+    static std::mutex guard;
+    std::lock_guard<std::mutex> hold(guard);
+    int dev = 0;
+    B200AMP_CUDA(cudaGetDevice(&dev));
+    B200AMP_REQUIRE(dev >= 0 && dev < MAX_DEVICES, "device index %d out of range", dev);
+    CopyLanes &l = lanes[dev];
+    if (!l.ready)
+    {
+        B200AMP_CUDA(cudaEventCreateWithFlags(&l.start, cudaEventDisableTiming));
+        for (int k = 0; k < MAX_LANES; k++)
+        {
+            B200AMP_CUDA(cudaStreamCreateWithFlags(&l.stream[k], cudaStreamNonBlocking));
+            B200AMP_CUDA(cudaEventCreateWithFlags(&l.done[k], cudaEventDisableTiming));
+            for (int i = 0; i < MAX_PIECES; i++)
+            {
+                B200AMP_CUDA(cudaEventCreateWithFlags(&l.piece[i][k], cudaEventDisableTiming));
+            }
+        }
+        l.ready = true;
+    }
+    *out = &l;
+    return B200AMP_OK;
+}
+
+static int clamp_pieces(int pieces, long long units)
+{
+    pieces = pieces < 1 ? 1 : pieces;
+    pieces = pieces > MAX_PIECES ? MAX_PIECES : pieces;
+    return pieces > units ? static_cast<int>(units) : pieces;
+}
+
+static int lane_count(int nranks)
+{
+    int lanes = tunables().ce_lanes;
+    lanes = lanes < 1 ? 1 : (lanes > MAX_LANES ? MAX_LANES : lanes);
+    return lanes > nranks - 1 ? (nranks > 1 ? nranks - 1 : 1) : lanes;
+}
+
+} // namespace b200amp
+
+extern "C" B200AMP_API int b200amp_rs_pass1_f16_ce(const void *const *grads16_by_rank, int nranks, int my_rank,
+                                                   void *staging16, void *reduced16, long long n, int pieces,
+                                                   const b200amp_step_state *st, void *workspace,
+                                                   double *const *pair_table_by_rank,
+                                                   const b200amp_zero1_sync *sync, b200amp_stream s)
+{
+    int rc = check_ranks(nranks, my_rank, "rs_pass1_ce");
+    if (rc != B200AMP_OK)
+    {
+        return rc;
+    }
+    B200AMP_REQUIRE(grads16_by_rank != nullptr && n > 0 && n % 8 == 0, "rs_pass1_ce: null pointer list or n = %lld "
+                                                                       "not a positive multiple of 8", n);
+    B200AMP_REQUIRE(nranks == 1 || (staging16 != nullptr && aligned(staging16, 16)),
+                    "rs_pass1_ce: the staging buffer ((nranks - 1) * n fp16 values) is null or not 16-byte aligned");
+    for (int r = 0; r < nranks; r++)
+    {
+        B200AMP_REQUIRE(grads16_by_rank[r] != nullptr, "rs_pass1_ce: gradient pointer of rank %d is null", r);
+    }
+    CopyLanes *lanes = nullptr;
+    rc = copy_lanes(&lanes);
+    if (rc != B200AMP_OK)
+    {
+        return rc;
+    }
+    const int nlanes = lane_count(nranks);
+    const P1Partition part = p1_partition(n / 8);
+    const long long per = part.vec_per_vblock * 8;             // elements per virtual block
+    pieces = clamp_pieces(pieces, part.vblocks);
+    cudaStream_t stream = as_stream(s);
+
+    if (sync != nullptr)
+    {
+        // every rank's gradients are in its arena before the first byte is pulled
+        rc = b200amp_zero1_barrier(sync, nranks, my_rank, SYNC_PHASE_GRADS, 3, s);
+        if (rc != B200AMP_OK)
+        {
+            return rc;
+        }
+    }
+    // what the kernel reads: this rank's own arena, and the staging slot of every peer. Peer
+    // (my_rank + k) % nranks uses slot k - 1.
+    const void *local_src[MAX_RANKS] = {};
+    char *staging = static_cast<char *>(staging16);
+    for (int k = 0; k < nranks; k++)
+    {
+        const int r = (my_rank + k) % nranks;
+        local_src[r] = k == 0 ? grads16_by_rank[r] : staging + static_cast<size_t>(k - 1) * n * 2;
+    }
+    // the copies start when everything enqueued on s so far has completed
+    B200AMP_CUDA(cudaEventRecord(lanes->start, stream));
+    bool forked[MAX_LANES] = {};
+    int turn = 0;
+    for (int i = 0; i < pieces; i++)
+    {
+        const int vb0 = static_cast<int>(static_cast<long long>(part.vblocks) * i / pieces);
+        const int vb1 = static_cast<int>(static_cast<long long>(part.vblocks) * (i + 1) / pieces);
+        const long long e0 = vb0 * per;
+        const long long e1 = vb1 * per < n ? vb1 * per : n;
+        bool used[MAX_LANES] = {};
+        for (int k = 1; k < nranks; k++)
+        {
+            const int peer = (my_rank + k) % nranks;            // every rank pulls from a different peer at a time
+            const int lane = turn++ % nlanes;
+            if (!forked[lane])
+            {
+                B200AMP_CUDA(cudaStreamWaitEvent(lanes->stream[lane], lanes->start, 0));
+                forked[lane] = true;
+            }
+            B200AMP_CUDA(cudaMemcpyAsync(staging + (static_cast<size_t>(k - 1) * n + e0) * 2,
+                                         static_cast<const char *>(grads16_by_rank[peer]) + e0 * 2,
+                                         static_cast<size_t>(e1 - e0) * 2, cudaMemcpyDefault, lanes->stream[lane]));
+            used[lane] = true;
+        }
+        for (int k = 0; k < nlanes; k++)
+        {
+            if (used[k])
+            {
+                B200AMP_CUDA(cudaEventRecord(lanes->piece[i][k], lanes->stream[k]));
+                B200AMP_CUDA(cudaStreamWaitEvent(stream, lanes->piece[i][k], 0));
+            }
+        }
+        const bool last = i == pieces - 1;
+        rc = rs_pass1_launch(local_src, nranks, my_rank, reduced16, n, vb0, vb1 - vb0, last ? 1 : 0, st, workspace,
+                             pair_table_by_rank, sync, last ? SYNC_SIGNAL_PAIRS : 0, s);
+        if (rc != B200AMP_OK)
+        {
+            return rc;
+        }
+    }
+    return B200AMP_OK;
+}
+
+extern "C" B200AMP_API int b200amp_pass2_ag_f16_ce(float *master, float *m, float *v, const void *reduced16,
+                                                   void *const *weights16_by_rank, int nranks, int my_rank,
+                                                   long long n, long long arena_offset,
+                                                   const b200amp_tensor_info *tensors, int ntensors,
+                                                   const b200amp_step_state *st, float beta1, float beta2, float eps,
+                                                   int pieces, b200amp_stream s)
+{
+    int rc = check_ranks(nranks, my_rank, "pass2_ag_ce");
+    if (rc != B200AMP_OK)
+    {
+        return rc;
+    }
+    B200AMP_REQUIRE(master != nullptr && m != nullptr && v != nullptr && reduced16 != nullptr &&
+                        weights16_by_rank != nullptr,
+                    "pass2_ag_ce: null pointer");
+    B200AMP_REQUIRE(n > 0 && n % 8 == 0, "pass2_ag_ce: n = %lld must be a positive multiple of 8", n);
+    for (int r = 0; r < nranks; r++)
+    {
+        B200AMP_REQUIRE(weights16_by_rank[r] != nullptr && aligned(weights16_by_rank[r], 16),
+                        "pass2_ag_ce: weight pointer of rank %d is null or not 16-byte aligned", r);
+    }
+    CopyLanes *lanes = nullptr;
+    rc = copy_lanes(&lanes);
+    if (rc != B200AMP_OK)
+    {
+        return rc;
+    }
+    const int nlanes = lane_count(nranks);
+    constexpr long long UNIT = 1024;                            // pieces start at multiples of 1024 elements
+    const long long units = (n + UNIT - 1) / UNIT;
+    pieces = clamp_pieces(pieces, units);
+    cudaStream_t stream = as_stream(s);
+    char *mine = static_cast<char *>(weights16_by_rank[my_rank]);
+    const char *grads = static_cast<const char *>(reduced16);
+    int turn = 0;
+    bool used[MAX_LANES] = {};
+    for (int i = 0; i < pieces; i++)
+    {
+        const long long e0 = units * i / pieces * UNIT;
+        const long long e1 = i == pieces - 1 ? n : units * (i + 1) / pieces * UNIT;
+        rc = b200amp_pass2_f16(master + e0, m + e0, v + e0, grads + e0 * 2, mine + e0 * 2, e1 - e0, arena_offset + e0,
+                               tensors, ntensors, st, beta1, beta2, eps, s);
+        if (rc != B200AMP_OK)
+        {
+            return rc;
+        }
+        if (nranks == 1)
+        {
+            continue;
+        }
+        // A skipped step leaves the slice as it was; the copies then rewrite the peers' arenas
+        // with the bytes they already hold, which costs link time but keeps the host free of any
+        // read of the state.
+        B200AMP_CUDA(cudaEventRecord(lanes->piece[i][0], stream));
+        for (int k = 1; k < nranks; k++)
+        {
+            const int peer = (my_rank + k) % nranks;
+            const int lane = turn++ % nlanes;
+            B200AMP_CUDA(cudaStreamWaitEvent(lanes->stream[lane], lanes->piece[i][0], 0));
+            B200AMP_CUDA(cudaMemcpyAsync(static_cast<char *>(weights16_by_rank[peer]) + e0 * 2, mine + e0 * 2,
+                                         static_cast<size_t>(e1 - e0) * 2, cudaMemcpyDefault, lanes->stream[lane]));
+            used[lane] = true;
+        }
+    }
+    // s continues when every push has landed
+    for (int k = 0; k < nlanes; k++)
+    {
+        if (used[k])
+        {
+            B200AMP_CUDA(cudaEventRecord(lanes->done[k], lanes->stream[k]));
+            B200AMP_CUDA(cudaStreamWaitEvent(stream, lanes->done[k], 0));
+        }
+    }
     return B200AMP_OK;
 }

@@ -235,14 +235,41 @@ B200AMP_API int b200amp_pass2_f16(float *master, float *m, float *v, const void 
                       long long arena_offset, const b200amp_tensor_info *tensors, int ntensors,
                       const b200amp_step_state *st, float beta1, float beta2, float eps, b200amp_stream s);
 
+/* Pass 2 with the decay flags handed over as a kernel parameter instead of a table in device
+ * memory. Only a CHANGE of the decay flag matters to the update, so the tensor table reduces to
+ * runs of equal flag (a GPT layout: 8 runs per layer + 3): b200amp_decay_runs_build merges a HOST
+ * copy of the table (checked as b200amp_check_tensor_table does) into at most B200AMP_MAX_RUNS
+ * runs, or returns B200AMP_ERR_LIMIT when there are more (then use b200amp_pass2_f16). The
+ * kernel then needs no shared memory and no table-loading prologue. Same arithmetic and the same
+ * bits as b200amp_pass2_f16; `runs` is a HOST pointer, read before the call returns. No
+ * reference counterpart beyond cuda/kernels/adamw_multi.cu:55-69 (the per-vector table search
+ * this replaces). */
+#define B200AMP_MAX_RUNS 256
+typedef struct b200amp_decay_runs
+{
+    unsigned int first4[B200AMP_MAX_RUNS];  /* first element of run k, divided by 4 */
+    int nruns;
+    int flag0;                              /* decay flag of run 0; run k has flag0 ^ (k & 1) */
+} b200amp_decay_runs;
+B200AMP_API int b200amp_decay_runs_build(const b200amp_tensor_info *host_table, int ntensors,
+                                         b200amp_decay_runs *out);
+B200AMP_API int b200amp_pass2_f16_runs(float *master, float *m, float *v, const void *grads16, void *weights16,
+                                       long long n, long long arena_offset, const b200amp_decay_runs *runs,
+                                       const b200amp_step_state *st, float beta1, float beta2, float eps,
+                                       b200amp_stream s);
+
 /* ---------------------------------------------------------------- ZeRO-1 with the collectives folded in
- * For R = 1, 2, 4 or 8 GPUs of one NVLink box, one process per GPU, with every rank's fp16
- * gradient arena, fp16 weight arena and pair table mapped into every process (CUDA IPC /
- * symmetric memory: the pointers below are ordinary device pointers of the CALLING process).
- * The reference has no multi-GPU code; per element these are pass 1 and pass 2 above. Neither
- * kernel waits on another GPU: the caller orders the ranks with stream-ordered barriers
- * (gradients of all ranks ready -> rs_pass1; all rs_pass1 done -> finalize_sums; all pass2_ag
- * done -> weights may be read). All remote accesses are plain 128-bit loads and stores. */
+ * For R = 1, 2, 4 or 8 GPUs of one NVLink box, with every rank's fp16 gradient arena, fp16
+ * weight arena and pair table addressable from every rank (one process with peer access on, or
+ * one process per GPU with the buffers mapped through CUDA IPC / symmetric memory: the pointers
+ * below are ordinary device pointers of the CALLING process). The reference has no multi-GPU
+ * code; per element these are pass 1 and pass 2 above. All remote accesses are plain 128-bit
+ * loads and stores, or cudaMemcpyAsync in the ..._ce forms; nothing uses multicast.
+ *
+ * Ordering between the ranks (gradients of all ranks ready -> rs_pass1; all pairs written ->
+ * finalize; all weights written -> the next forward pass) is either the caller's (the plain
+ * entry points: a one-process host puts events between the ranks' streams) or the library's
+ * (the ..._sync entry points and b200amp_zero1_barrier, below). */
 
 /* Reduce-scatter + pass 1. grads16_by_rank[r] (HOST array of nranks device pointers) is the
  * start of THIS rank's slice in rank r's gradient arena. The slice is averaged over the ranks
@@ -254,6 +281,22 @@ B200AMP_API int b200amp_rs_pass1_f16(const void *const *grads16_by_rank, int nra
                                      long long n, const b200amp_step_state *st, void *workspace,
                                      double *const *pair_table_by_rank, b200amp_stream s);
 
+/* The same reduction in parts, for a caller that reduces a slice piece by piece (for instance
+ * while the next piece is still on its way into a local staging buffer). The slice's norm is
+ * summed over a fixed partition into virtual blocks (b200amp_pass1_partition); one call reduces
+ * the elements of the virtual blocks vblock_first .. vblock_first + vblock_count - 1 and keeps
+ * their partial sums in the workspace. The pointers still address the start of the slice. The
+ * call with last_part != 0 must come last on the stream: it adds ALL partials of the slice and
+ * writes the pairs, so the calls together give the bits of b200amp_rs_pass1_f16. */
+B200AMP_API int b200amp_rs_pass1_f16_part(const void *const *grads16_by_rank, int nranks, int my_rank,
+                                          void *reduced16, long long n, int vblock_first, int vblock_count,
+                                          int last_part, const b200amp_step_state *st, void *workspace,
+                                          double *const *pair_table_by_rank, b200amp_stream s);
+
+/* The fixed partition pass 1 sums over: a range of n elements has *vblocks virtual blocks of
+ * *elements_per_vblock elements (the last may be shorter). A function of n alone. Host only. */
+B200AMP_API int b200amp_pass1_partition(long long n, int *vblocks, long long *elements_per_vblock);
+
 /* Pass 2 + all-gather. As b200amp_pass2_f16 on the rank's slice, with the fp16 weights stored
  * to weights16_by_rank[r] for every r (HOST array of nranks device pointers: the start of this
  * rank's slice in rank r's weight arena, the rank's own arena included). */
@@ -261,6 +304,81 @@ B200AMP_API int b200amp_pass2_ag_f16(float *master, float *m, float *v, const vo
                                      void *const *weights16_by_rank, int nranks, long long n, long long arena_offset,
                                      const b200amp_tensor_info *tensors, int ntensors, const b200amp_step_state *st,
                                      float beta1, float beta2, float eps, b200amp_stream s);
+
+/* ---- ordering between one-process-per-GPU ranks, owned by the library
+ * Each rank owns one block of B200AMP_ZERO1_SYNC_BYTES bytes of device memory that every rank
+ * has mapped, zeroed with b200amp_zero1_sync_init before any rank's first step (the ranks agree
+ * on that on the host, once). A rank announces a phase of the step in flight by storing the
+ * step's number into its word of every rank's block; a rank waits by polling its own block. The
+ * step's number lives in the block and is advanced on the device, so a step is the same
+ * sequence of launches every time. Phases: 0 gradients ready, 1 pairs written, 2 weights
+ * written.
+ * Every wait is bounded (wait_limit polls; 0 = the default, about one second). A wait that runs
+ * out records (phase + 1) | missing_rank << 8 in the block's error word, sets bit 1 of
+ * b200amp_device_error, and the kernel returns without doing its work; kernels launched after
+ * it see the error word and return at once, the finalize sets found_inf = 1 so that pass 2
+ * changes nothing, and the step counter is not advanced. Nothing traps or spins for ever. After
+ * a reported give-up the optimizer's state is not to be trusted: restore a checkpoint, zero
+ * every rank's block and workspace again, and go on. */
+#define B200AMP_ZERO1_SYNC_BYTES 256
+typedef struct b200amp_zero1_sync
+{
+    void *block_by_rank[8];     /* block_by_rank[r]: rank r's block, a device pointer of the calling process */
+    unsigned int wait_limit;    /* polls before a wait gives up; 0 = default */
+} b200amp_zero1_sync;
+enum
+{
+    B200AMP_SYNC_SIGNAL = 1,    /* announce the phase to every rank */
+    B200AMP_SYNC_WAIT = 2,      /* wait for every rank's announcement of the phase */
+    B200AMP_SYNC_ADVANCE = 4    /* the step is over on this rank: advance its step counter */
+};
+B200AMP_API int b200amp_zero1_sync_init(void *block, b200amp_stream s);
+/* Synchronous read of a rank's own block: steps completed, and the error word (0 = none). */
+B200AMP_API int b200amp_zero1_sync_read(const void *block, unsigned int *steps_done, unsigned int *error);
+/* One small kernel: `what` is a combination of the three flags above, applied to `phase` of the
+ * step in flight. The step's last launch is (phase 2, SIGNAL | WAIT | ADVANCE): enqueued after
+ * pass2_ag, it tells every rank that this rank's weights have landed and returns when every
+ * rank's have landed here. */
+B200AMP_API int b200amp_zero1_barrier(const b200amp_zero1_sync *sync, int nranks, int my_rank, int phase, int what,
+                                      b200amp_stream s);
+/* b200amp_rs_pass1_f16 that orders itself: every CTA announces this rank's gradients (phase 0)
+ * and waits for every rank's before it loads anything; the last CTA announces the pairs it has
+ * written (phase 1). */
+B200AMP_API int b200amp_rs_pass1_f16_sync(const void *const *grads16_by_rank, int nranks, int my_rank,
+                                          void *reduced16, long long n, const b200amp_step_state *st,
+                                          void *workspace, double *const *pair_table_by_rank,
+                                          const b200amp_zero1_sync *sync, b200amp_stream s);
+/* b200amp_finalize_sums that first waits (phase 1) for every rank's pair; sums is this rank's
+ * pair table. */
+B200AMP_API int b200amp_finalize_sums_sync(b200amp_step_state *st, const double *sums, int nranks, int my_rank,
+                                           const b200amp_schedule *cfg, b200amp_step_state *history,
+                                           int history_len, const b200amp_zero1_sync *sync, b200amp_stream s);
+
+/* ---- copy-engine forms: same results bit for bit, but the bytes that cross NVLink are moved by
+ * cudaMemcpyAsync on copy streams of the library instead of by loads and stores of the kernels,
+ * piece by piece, overlapped with the kernels (which then touch local memory only). With both
+ * directions of the links busy the copy engines move 771-776 GB/s per direction between two
+ * B200s where SM-issued loads reach 664 and stores 704.
+ * rs: staging16 is a local buffer of (nranks - 1) * n fp16 values; the peers' slices are pulled
+ * into it while earlier pieces are reduced. With sync != null the call starts with the phase-0
+ * exchange and its last piece announces phase 1 (as b200amp_rs_pass1_f16_sync); with sync == null
+ * the caller has ordered the ranks. ag: every piece of fp16 weights is pushed into the peers'
+ * arenas while pass 2 runs on the next piece; the call returns with s waiting for the last push.
+ * pieces: 1..64. Work enqueued on s before the call is complete before the first copy starts.
+ * The streams and events are created on the first call on a device and kept (these two calls
+ * allocate); one host thread per device may use them. */
+B200AMP_API int b200amp_rs_pass1_f16_ce(const void *const *grads16_by_rank, int nranks, int my_rank, void *staging16,
+                                        void *reduced16, long long n, int pieces, const b200amp_step_state *st,
+                                        void *workspace, double *const *pair_table_by_rank,
+                                        const b200amp_zero1_sync *sync, b200amp_stream s);
+B200AMP_API int b200amp_pass2_ag_f16_ce(float *master, float *m, float *v, const void *reduced16,
+                                        void *const *weights16_by_rank, int nranks, int my_rank, long long n,
+                                        long long arena_offset, const b200amp_tensor_info *tensors, int ntensors,
+                                        const b200amp_step_state *st, float beta1, float beta2, float eps, int pieces,
+                                        b200amp_stream s);
+/* cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, s): a copy-engine transfer between any two
+ * device pointers of the calling process, a peer's mapped memory included. */
+B200AMP_API int b200amp_copy_async(void *dst, const void *src, long long bytes, b200amp_stream s);
 
 /* The whole step for an arena held by one GPU: b200amp_pass1_finalize_f16 then
  * b200amp_pass2_f16 (two launches). */
@@ -285,9 +403,10 @@ B200AMP_API int b200amp_graph_destroy(b200amp_graph *g);
  * Process-wide and unsynchronised: set them before other threads launch work. */
 B200AMP_API int b200amp_tune_set(const char *key, int value);
 B200AMP_API int b200amp_tune_get(const char *key, int *value);
-/* *out = 1 if a kernel of this library on the current device gave up a bounded wait (a bulk
- * copy that never completed) since the last call, else 0; reading clears the flag.
- * Synchronises the device. */
+/* *out = what gave up a bounded wait on the current device since the last call, as a bit mask:
+ * 1 a shared-memory staged pass 2 waiting for a bulk copy that never completed, 2 a ZeRO-1
+ * kernel waiting for another rank; 0 = nothing. Reading clears it. Synchronises the device.
+ * After a nonzero answer the optimizer state of the step that gave up is not to be trusted. */
 B200AMP_API int b200amp_device_error(int *out);
 /* Kernel launches enqueued by this library on the calling process so far. */
 B200AMP_API long long b200amp_launch_count(void);

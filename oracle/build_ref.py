@@ -2,6 +2,9 @@
 
     python oracle/build_ref.py [/path/to/cuda-transformer]
 
+The checkout is the argument, else $B200AMP_REFERENCE_DIR, else a directory named
+`reference` beside this repository.
+
 Sources are compiled where they lie in the reference checkout (cuda/kernels/scaler.cu,
 cuda/kernels/adamw_multi.cu, with -DFP16 as the reference's fp16 build, Makefile:44-48,
 only the arch flag changed from sm_75 to sm_100a); oracle/ref_wrap.cu adds extern "C"
@@ -19,11 +22,16 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
 LIB_PATH = os.path.join(OUT_DIR, "libref_amp.so")
-DEFAULT_REF = "/root/reference"
 
 
-def build(ref_root: str = DEFAULT_REF, force: bool = False):
+def default_ref() -> str:
+    """Where the reference checkout is looked for when no path is given."""
+    return os.environ.get("B200AMP_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def build(ref_root: str = None, force: bool = False):
     """Path of the built library, or None if the reference checkout is absent."""
+    ref_root = ref_root or default_ref()
     srcs = [os.path.join(ref_root, "cuda", "kernels", f) for f in ("scaler.cu", "adamw_multi.cu")]
     if not all(os.path.exists(s) for s in srcs):
         return LIB_PATH if os.path.exists(LIB_PATH) else None
@@ -44,4 +52,4 @@ def build(ref_root: str = DEFAULT_REF, force: bool = False):
 
 
 if __name__ == "__main__":
-    print(build(sys.argv[1] if len(sys.argv) > 1 else DEFAULT_REF, force=True))
+    print(build(sys.argv[1] if len(sys.argv) > 1 else None, force=True))

@@ -35,7 +35,6 @@ BIN = os.path.join(OUT, "bin")
 DUMP = os.path.join(OUT, "data", "debug.bin")
 ROUNDTRIP = os.path.join(BIN, "ckpt_roundtrip")
 WEIGHTS_ROUNDTRIP = os.path.join(BIN, "weights_roundtrip")
-DEFAULT_REF = "/root/reference"
 REPLACED = ("kernels/scaler.cu", "kernels/adamw_multi.cu", "graph.cu")
 PROGRAMS = ("test_fast", "test_checkpoint")
 TRAINER = "train_fast"
@@ -121,8 +120,11 @@ def write_dump(ref_root: str) -> str:
     return DUMP
 
 
-def build(ref_root: str = DEFAULT_REF, jobs: int = 8):
+def build(ref_root: str = None, jobs: int = 8):
     """Dict name -> path of the four binaries, or None without the reference checkout."""
+    if ref_root is None:
+        from oracle.build_ref import default_ref
+        ref_root = default_ref()
     cuda = os.path.join(ref_root, "cuda")
     if not os.path.exists(os.path.join(cuda, "gpt_fast.cu")):
         return binaries() if available() else None
@@ -196,4 +198,4 @@ def build(ref_root: str = DEFAULT_REF, jobs: int = 8):
 
 if __name__ == "__main__":
     sys.path.insert(0, REPO)
-    print(build(sys.argv[1] if len(sys.argv) > 1 else DEFAULT_REF))
+    print(build(sys.argv[1] if len(sys.argv) > 1 else None))

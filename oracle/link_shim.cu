@@ -80,10 +80,12 @@ void adamw_multi(float *params, floatX *params_x, const float *grads, float *m, 
 
 // ---- native (-DB200AMP_SHIM_NATIVE): the same three calls routed onto the fp16-arena step.
 // The reference's backward pass leaves loss-scaled fp32 gradients in its arena; unscale_and_norm
-// becomes the bridge (round to fp16 into an arena this shim keeps, pass 1 on the rounded values,
-// fp32 arena cleared behind it), finalize_step the finalize on the bridge's sums, adamw_multi the
-// native pass 2 on the fp16 arena. 10 + 28 B/param instead of 8 + 30 + the 4 B/param memset, and
-// the gradients the optimizer sees are rounded to fp16 first, so a run agrees with the stock
+// becomes the bridge (round to fp16 into an arena this shim keeps, pass 1 on the rounded values),
+// finalize_step the finalize on the bridge's sums, adamw_multi the native pass 2 on the fp16
+// arena. The fp32 arena is left for the reference's own grads.zero (cuda/gpt_fast.cu:455), which an
+// unmodified trainer still runs every step, so the bridge does not clear it a second time:
+// 6 + 28 B/param + the reference's 4 B/param memset, instead of 8 + 30 + 4. The
+// gradients the optimizer sees are rounded to fp16 first, so a run agrees with the stock
 // program to fp16 rounding of the gradients, not bit for bit; the fp32 arena is NOT unscaled in
 // place (test_fast reads it back, so the test programs use the compat shim). For train_fast.
 
@@ -125,7 +127,7 @@ static NativeArena &arena_for(const float *grads32, long long n, cudaStream_t s)
 void unscale_and_norm(float *grads, long long n, StepState *st, float *, cudaStream_t s)
 {
     NativeArena &a = arena_for(grads, n, s);
-    SHIM_CHECK(b200amp_cast_pass1_f32(grads, a.grads16, n, /*clear_source=*/1, abi(st), a.workspace, nullptr, nullptr,
+    SHIM_CHECK(b200amp_cast_pass1_f32(grads, a.grads16, n, /*clear_source=*/0, abi(st), a.workspace, nullptr, nullptr,
                                       0, s));
 }
 

@@ -92,17 +92,39 @@ class TorchAmpStep:
         return torch.cat(out)
 
 
+def _from_pool(pool: torch.Tensor, at: int, count: int) -> torch.Tensor:
+    """count values of the pool starting at `at`, wrapping around (a fresh tensor)."""
+    size = pool.numel()
+    at %= size
+    if at + count <= size:
+        return pool[at:at + count].clone()
+    reps = (at + count + size - 1) // size
+    return pool.repeat(reps)[at:at + count].clone()
+
+
 def time_cpu_step(shapes: Sequence[Tuple[int, ...]], steps: int = 5, warmup: int = 1, loss_scale: float = 32768.0,
                   seed: int = 0) -> dict:
     """Time the stock path (clip_grad_norm_) on the host cores with all torch threads.
-    Returns {"seconds_per_step", "params", "threads"}; gradient generation is outside the timer."""
+    Returns {"seconds_per_step", "params", "threads"}. Parameters and gradients are N(0, 0.02) and
+    N(0, 1e-3) * loss_scale drawn from one seeded pool of 2^26 normal values that the tensors
+    slice (with wrap-around): the distributions are the workload's, and drawing 1.3 G fresh
+    normals per step on one host thread would take longer than the steps being timed. Every step
+    sees the same fp16 gradients, widened to fp32 again before it (outside the timer: unscale_
+    overwrites .grad in place)."""
     gen = torch.Generator().manual_seed(seed)
-    init = [torch.randn(s, generator=gen) * 0.02 for s in shapes]
+    pool = torch.randn(1 << 26, generator=gen)
+    sizes = [int(torch.Size(s).numel()) for s in shapes]
+    init, grads, at = [], [], 0
+    for s, k in zip(shapes, sizes):
+        init.append((_from_pool(pool, at, k) * 0.02).reshape(s))
+        grads.append((_from_pool(pool, at + 12345, k) * (1e-3 * loss_scale)).half().reshape(s))
+        at += k
+    del pool
     ref = TorchAmpStep(shapes, init, loss_scale=loss_scale)
+    del init
     n = sum(p.numel() for p in ref.params)
     times = []
     for k in range(warmup + steps):
-        grads = [(torch.randn(s, generator=gen) * 1e-3 * ref.loss_scale()).half() for s in shapes]
         ref.set_grads(grads)
         t0 = time.perf_counter()
         ref.step()
@@ -110,4 +132,5 @@ def time_cpu_step(shapes: Sequence[Tuple[int, ...]], steps: int = 5, warmup: int
         if k >= warmup:
             times.append(dt)
     times.sort()
-    return {"seconds_per_step": times[len(times) // 2], "params": n, "threads": torch.get_num_threads()}
+    return {"seconds_per_step": times[len(times) // 2], "params": n, "threads": torch.get_num_threads(),
+            "steps": steps}

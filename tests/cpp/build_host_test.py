@@ -1,7 +1,8 @@
 """Builds the C++ test programs of the host layers (host-only C++ over the C ABI) into
 tests/cpp/bin/, linked against the in-tree libb200amp.so with an rpath relative to the binary:
 test_amp_host (one GPU: shim + AmpOptimizer), test_zero1_host (one process, R ranks) and the
-measurement program peer_bandwidth (two GPUs; plain CUDA, does not use the library)."""
+NVLink measurement program peer_bandwidth (two or more GPUs; plain CUDA, does not use the library; its output is
+checked by tests/test_gpu_host_cpp.py)."""
 from __future__ import annotations
 
 import os

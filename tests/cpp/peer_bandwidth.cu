@@ -1,5 +1,5 @@
 // peer_bandwidth.cu: what bounds a kernel that reads or writes another GPU's memory over NVLink.
-// A measurement program, not a test: it prints the bandwidth per direction of a 1 GiB copy between
+// It prints the bandwidth per direction of a 1 GiB copy between
 // GPU 0 and GPU 1 for each way of moving the bytes, first with one direction busy, then with both
 // GPUs copying against each other at once (the situation of the ZeRO-1 step, where every rank
 // pulls from and pushes to its peers at the same time):
@@ -10,8 +10,13 @@
 //   bulk           cp.async.bulk global -> shared -> global through a ring of stages, one thread
 //                  per CTA driving it (no multicast; every barrier wait bounded)
 //
-// One process, two devices, peer access on. Needs two GPUs; prints a note and exits 0 with fewer.
-// Built by tests/cpp/build_host_test.py.
+// With four or eight GPUs a second table follows: the all-to-all pattern of the ZeRO-1 step at that
+// rank count (every GPU exchanges one slice with each of its R - 1 peers at the same time, 256 MiB
+// per pair), inbound GB/s per GPU, for the copy engines (one stream per peer) and for one kernel
+// per GPU that issues the loads or the stores itself.
+//
+// One process, peer access on. Needs two GPUs; prints a note and exits 0 with fewer.
+// Built by tests/cpp/build_host_test.py; run and checked by tests/test_gpu_host_cpp.py.
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -291,6 +296,216 @@ static void run(Mover how, bool read, Side &x, Side &y, bool both, double out[2]
     }
 }
 
+// ---------------------------------------------------------------- all-to-all among R GPUs
+
+constexpr long long SLICE = 256LL << 20;        // bytes each pair of GPUs exchanges per direction
+constexpr int MAX_R = 8;
+
+struct PeerList
+{
+    const float *src[MAX_R - 1];
+    float *dst[MAX_R - 1];
+    int count;
+};
+
+// One kernel moves all R - 1 slices: the loads of a trip are issued together, then the stores.
+// Pull: src on the peers, dst local. Push: src local, dst on the peers.
+__global__ void __launch_bounds__(256) a2a_copy(PeerList p, long long n8)
+{
+    const long long stride = static_cast<long long>(gridDim.x) * 256;
+    for (long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x; i < n8; i += stride)
+    {
+        Float8 v[MAX_R - 1];
+#pragma unroll
+        for (int k = 0; k < MAX_R - 1; k++)
+        {
+            if (k < p.count)
+            {
+                v[k] = load8(p.src[k] + i * 8);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < MAX_R - 1; k++)
+        {
+            if (k < p.count)
+            {
+                store8(p.dst[k] + i * 8, v[k]);
+            }
+        }
+    }
+}
+
+struct Node
+{
+    char *src = nullptr, *dst = nullptr;        // R slices each: slice q is what goes to / came from GPU q
+    cudaStream_t main = nullptr, lane[MAX_R - 1] = {};
+    cudaEvent_t begin = nullptr, end = nullptr, done[MAX_R - 1] = {};
+};
+
+// mode 0: copy engine pull, 1: copy engine push, 2: SM loads (pull), 3: SM stores (push).
+// Prints the slowest and the fastest GPU's inbound GB/s.
+static void all_to_all(Node *nodes, int R, int mode, const char *label)
+{
+    const int reps = 3;
+    for (int pass = 0; pass < 2; pass++)        // pass 0 warms up
+    {
+        for (int g = 0; g < R; g++)
+        {
+            CK(cudaSetDevice(g));
+            CK(cudaEventRecord(nodes[g].begin, nodes[g].main));
+        }
+        for (int i = 0; i < reps; i++)
+        {
+            for (int g = 0; g < R; g++)
+            {
+                CK(cudaSetDevice(g));
+                Node &me = nodes[g];
+                if (mode < 2)
+                {
+                    for (int k = 1; k < R; k++)
+                    {
+                        const int q = (g + k) % R;
+                        if (i == 0)
+                        {
+                            CK(cudaStreamWaitEvent(me.lane[k - 1], me.begin, 0));
+                        }
+                        if (mode == 0)
+                        {
+                            CK(cudaMemcpyAsync(me.dst + q * SLICE, nodes[q].src + g * SLICE, SLICE, cudaMemcpyDefault,
+                                               me.lane[k - 1]));
+                        }
+                        else
+                        {
+                            CK(cudaMemcpyAsync(nodes[q].dst + g * SLICE, me.src + q * SLICE, SLICE, cudaMemcpyDefault,
+                                               me.lane[k - 1]));
+                        }
+                    }
+                }
+                else
+                {
+                    PeerList p = {};
+                    p.count = R - 1;
+                    for (int k = 1; k < R; k++)
+                    {
+                        const int q = (g + k) % R;
+                        p.src[k - 1] = reinterpret_cast<const float *>(mode == 2 ? nodes[q].src + g * SLICE
+                                                                                 : me.src + q * SLICE);
+                        p.dst[k - 1] = reinterpret_cast<float *>(mode == 2 ? me.dst + q * SLICE
+                                                                           : nodes[q].dst + g * SLICE);
+                    }
+                    a2a_copy<<<148 * 4, 256, 0, me.main>>>(p, SLICE / 32);
+                    CK(cudaGetLastError());
+                }
+            }
+        }
+        for (int g = 0; g < R; g++)
+        {
+            CK(cudaSetDevice(g));
+            Node &me = nodes[g];
+            if (mode < 2)
+            {
+                for (int k = 0; k < R - 1; k++)
+                {
+                    CK(cudaEventRecord(me.done[k], me.lane[k]));
+                    CK(cudaStreamWaitEvent(me.main, me.done[k], 0));
+                }
+            }
+            CK(cudaEventRecord(me.end, me.main));
+        }
+        for (int g = 0; g < R; g++)
+        {
+            CK(cudaSetDevice(g));
+            CK(cudaStreamSynchronize(nodes[g].main));
+        }
+    }
+    double lo = 1e30, hi = 0.0;
+    for (int g = 0; g < R; g++)
+    {
+        float ms = 0.0f;
+        CK(cudaEventElapsedTime(&ms, nodes[g].begin, nodes[g].end));
+        const double gbs = static_cast<double>(SLICE) * (R - 1) * reps / (ms * 1e-3) / 1e9;
+        lo = gbs < lo ? gbs : lo;
+        hi = gbs > hi ? gbs : hi;
+    }
+    printf("all-to-all R=%d %-28s %8.1f .. %8.1f\n", R, label, lo, hi);
+}
+
+static int all_to_all_tables(int count)
+{
+    for (int R = 4; R <= MAX_R && R <= count; R *= 2)
+    {
+        for (int a = 0; a < R; a++)
+        {
+            for (int b = 0; b < R; b++)
+            {
+                int can = 1;
+                if (a != b)
+                {
+                    CK(cudaDeviceCanAccessPeer(&can, a, b));
+                }
+                if (!can)
+                {
+                    printf("GPU %d cannot map GPU %d: no all-to-all table for R=%d\n", a, b, R);
+                    return 0;
+                }
+            }
+        }
+        Node nodes[MAX_R];
+        for (int g = 0; g < R; g++)
+        {
+            CK(cudaSetDevice(g));
+            for (int q = 0; q < R; q++)
+            {
+                if (q != g)
+                {
+                    cudaError_t err = cudaDeviceEnablePeerAccess(q, 0);
+                    if (err != cudaSuccess && err != cudaErrorPeerAccessAlreadyEnabled)
+                    {
+                        CK(err);
+                    }
+                    cudaGetLastError();
+                }
+            }
+            Node &me = nodes[g];
+            CK(cudaMalloc(&me.src, SLICE * R));
+            CK(cudaMalloc(&me.dst, SLICE * R));
+            CK(cudaMemset(me.src, g + 1, SLICE * R));
+            CK(cudaMemset(me.dst, 0, SLICE * R));
+            CK(cudaStreamCreate(&me.main));
+            CK(cudaEventCreate(&me.begin));
+            CK(cudaEventCreate(&me.end));
+            for (int k = 0; k < R - 1; k++)
+            {
+                CK(cudaStreamCreateWithFlags(&me.lane[k], cudaStreamNonBlocking));
+                CK(cudaEventCreateWithFlags(&me.done[k], cudaEventDisableTiming));
+            }
+            CK(cudaDeviceSynchronize());
+        }
+        printf("\nall-to-all among %d GPUs, %lld MiB per pair and direction, inbound GB/s per GPU (slowest .. fastest)\n",
+               R, SLICE >> 20);
+        all_to_all(nodes, R, 0, "copy engine, pull");
+        all_to_all(nodes, R, 1, "copy engine, push");
+        all_to_all(nodes, R, 2, "SM loads (pull)");
+        all_to_all(nodes, R, 3, "SM stores (push)");
+        // the last mode pushed: slice g of GPU q's destination holds GPU g's pattern
+        unsigned char got = 0;
+        CK(cudaSetDevice(1));
+        CK(cudaMemcpy(&got, nodes[1].dst + 0 * SLICE + SLICE - 1, 1, cudaMemcpyDeviceToHost));
+        if (got != 1)
+        {
+            printf("all-to-all R=%d: wrong byte %d in a destination (expected 1)\n", R, got);
+            return 1;
+        }
+        for (int g = 0; g < R; g++)
+        {
+            CK(cudaSetDevice(g));
+            CK(cudaFree(nodes[g].src));
+            CK(cudaFree(nodes[g].dst));
+        }
+    }
+    return 0;
+}
+
 int main()
 {
     int count = 0;
@@ -332,5 +547,15 @@ int main()
     CK(cudaMemcpy(&tail0, x.b + BYTES - 1, 1, cudaMemcpyDeviceToHost));
     CK(cudaMemcpy(&tail1, y.b + BYTES - 1, 1, cudaMemcpyDeviceToHost));
     printf("\nlast byte of each destination: %d and %d (expected 2 and 1)\n", tail0, tail1);
-    return (tail0 == 2 && tail1 == 1) ? 0 : 1;
+    if (tail0 != 2 || tail1 != 1)
+    {
+        return 1;
+    }
+    CK(cudaSetDevice(0));
+    CK(cudaFree(x.a));
+    CK(cudaFree(x.b));
+    CK(cudaSetDevice(1));
+    CK(cudaFree(y.a));
+    CK(cudaFree(y.b));
+    return all_to_all_tables(count);
 }

@@ -170,4 +170,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2 and not os.environ.get("B200AMP_REFERENCE_DIR"):
+        sys.exit("usage: make_golden.py /path/to/cuda-transformer   (or set B200AMP_REFERENCE_DIR)")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ["B200AMP_REFERENCE_DIR"])

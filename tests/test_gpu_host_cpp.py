@@ -1,4 +1,4 @@
-"""Runs the C++ host-layer test program (tests/cpp/test_amp_host.cpp) on the GPU."""
+"""Runs the C++ host-layer test programs (tests/cpp/) on the GPU."""
 import os
 import subprocess
 import sys
@@ -43,3 +43,37 @@ def test_cpp_zero1_host_program_checks_pass():
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-2000:]
     assert "all checks passed" in proc.stdout and "FAILED" not in proc.stdout
     assert proc.stdout.count(" ok\n") == 4 * 10
+
+
+@pytest.mark.gpu
+def test_peer_bandwidth_program_reports_sane_nvlink_figures():
+    """tests/cpp/peer_bandwidth.cu: on one GPU it says so and measures nothing; on two or more every
+    mover's figure must be a plausible NVLink rate and the copied bytes must have arrived; on four
+    or eight the all-to-all table of the ZeRO-1 pattern must be there too."""
+    import re
+
+    import torch
+
+    import build_host_test
+    exe = build_host_test.build(program="peer_bandwidth")
+    proc = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    sys.stdout.write(proc.stdout)
+    sys.stderr.write(proc.stderr)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-2000:]
+    count = torch.cuda.device_count()
+    if count < 2:
+        assert "nothing measured" in proc.stdout
+        return
+    if "cannot map" in proc.stdout:
+        return
+    rows = re.findall(r"^(copy engine|SM ld / st \(256-bit\)|bulk through shared memory)\s+(read|write)\s+"
+                      r"([0-9.]+)\s+([0-9.]+) \|\s+([0-9.]+)", proc.stdout, re.M)
+    assert len(rows) == 6, proc.stdout
+    for name, way, one, both0, both1 in rows:
+        assert all(200.0 < float(x) < 1000.0 for x in (one, both0, both1)), (name, way, one, both0, both1)
+    assert "expected 2 and 1" in proc.stdout
+    if count >= 4:
+        table = re.findall(r"^all-to-all R=(\d) (.{28})\s+([0-9.]+) \.\.\s+([0-9.]+)", proc.stdout, re.M)
+        assert len(table) >= 4, proc.stdout
+        for r, label, lo, hi in table:
+            assert 100.0 < float(lo) <= float(hi) < 1000.0, (r, label, lo, hi)

@@ -253,6 +253,58 @@ def test_1024_tensors_and_boundaries_inside_a_group(G, O):
     compare_arrays(gpu2, ora2)
 
 
+@pytest.mark.parametrize("world", [1, 4])
+def test_decay_runs_as_a_kernel_parameter_give_the_bits_of_the_table_in_memory(G, world):
+    """b200amp_pass2_f16_runs against b200amp_pass2_f16: 400 tensors that merge into 256 runs (the
+    most the parameter form takes), edges at multiples of 4 inside 8-element groups, gaps between
+    tensors, whole arena and 4 shards addressed by their offsets; and a table of 258 runs is
+    refused by the builder, not truncated."""
+    from cuda_transformer_b200 import _lib, amp
+    rng = np.random.default_rng(11)
+    counts = rng.choice([4, 12, 20, 36, 260, 1028, 5000], size=400)
+    flags = []
+    for i in range(400):                                # the flag changes at two tensors out of three
+        flags.append((flags[-1] ^ 1) if i and i % 3 != 0 else (flags[-1] if i else 1))
+    changes = sum(1 for a, b in zip(flags, flags[1:]) if a != b)
+    for i in range(len(flags) - 1, 0, -1):              # 266 changes: undo the last ones until 255 are left (256 runs)
+        if changes <= 255:
+            break
+        if flags[i] != flags[i - 1]:
+            for j in range(i, len(flags)):
+                flags[j] ^= 1
+            changes -= 1
+    table, at = [], 0
+    for i, c in enumerate(counts):
+        table.append((at, int(c), int(flags[i])))
+        at += int(c) + (8 if i % 50 == 49 else 0)       # a gap now and then: it belongs to the run before it
+    runs = amp.decay_runs_build(table)
+    assert runs.nruns == 256
+    n = (at + 8 * world - 1) // (8 * world) * (8 * world)
+    init = (rng.standard_normal(n) * 0.5).astype(np.float32)
+    kw = dict(weight_decay=0.5, lr=1e-2, min_lr=1e-2)
+    a = G.GpuStep(init, table, sched(amp, **kw), loss_scale=256.0)
+    b = G.GpuStep(init, table, sched(amp, **kw), loss_scale=256.0)
+    per = n // world
+    for _ in range(2):
+        bits = (rng.standard_normal(n) * 1e-3 * 256.0).astype(np.float16).view(np.uint16)
+        for g in (a, b):
+            g.set_grads16(bits)
+            amp.pass1_finalize_f16(g.grads16, n, g.state, g.workspace, g.cfg, g.history, g.history_len)
+        for r in range(world):
+            sl = slice(r * per, (r + 1) * per)
+            amp.pass2_f16(a.master[sl], a.m[sl], a.v[sl], a.grads16[sl], a.weights16[sl], per, r * per, a.tensors,
+                          a.ntensors, a.state, a.cfg.beta1, a.cfg.beta2, a.eps)
+            amp.pass2_f16_runs(b.master[sl], b.m[sl], b.v[sl], b.grads16[sl], b.weights16[sl], per, r * per, runs,
+                               b.state, b.cfg.beta1, b.cfg.beta2, b.eps)
+    for x, y in zip(a.host(), b.host()):
+        assert np.array_equal(x, y)
+    assert bytes(a.read_state()) == bytes(b.read_state())
+    too_many = [(4 * i, 4, i % 2) for i in range(258)]
+    with pytest.raises(amp.B200AmpError, match="runs") as err:
+        amp.decay_runs_build(too_many)
+    assert err.value.status == _lib.ERR_LIMIT
+
+
 def test_zero_gradients_are_not_an_overflow(G, O):
     """An empty batch: grad_norm == 0.0 and the step is taken (cuda/tests/test_fast.cu:459-471)."""
     from cuda_transformer_b200 import amp

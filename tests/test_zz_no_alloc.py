@@ -75,3 +75,53 @@ def test_static_scratch_pass1_refuses_sizes_beyond_its_maximum():
     amp.pass1_f16_static(small, 8, state, out)                      # and the smallest size works
     torch.cuda.synchronize()
     assert out.cpu().tolist() == [0.0, 0.0]
+
+
+def test_static_scratch_pass1_refused_calls_leave_the_stream_and_the_scratch_alone():
+    """A call with a bad size, a null or a misaligned pointer is refused before anything is
+    enqueued: the answer of the next good call is what it would have been without them."""
+    from cuda_transformer_b200 import amp
+    n = 1 << 16
+    grads = _inputs(n, 3, 1024.0)
+    state = torch.frombuffer(bytearray(bytes(amp.initial_state(1024.0))), dtype=torch.uint8).cuda()
+    out = torch.full((2,), -1.0, dtype=torch.float64, device="cuda")
+    amp.pass1_f16_static(grads, n, state, out)
+    torch.cuda.synchronize()
+    want = out.cpu().numpy().copy()
+    out.fill_(-1.0)
+    torch.cuda.synchronize()
+    for bad_call in (lambda: amp.pass1_f16_static(grads, 0, state, out),
+                     lambda: amp.pass1_f16_static(grads, n + 4, state, out),
+                     lambda: amp.pass1_f16_static(None, n, state, out),
+                     lambda: amp.pass1_f16_static(grads, n, None, out),
+                     lambda: amp.pass1_f16_static(grads.data_ptr() + 2, n - 8, state, out)):
+        with pytest.raises(amp.B200AmpError):
+            bad_call()
+    torch.cuda.synchronize()
+    assert out.cpu().tolist() == [-1.0, -1.0], "a refused call wrote its output"
+    amp.pass1_f16_static(grads, n, state, out)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), want)
+
+
+def test_static_scratch_pass1_on_a_second_device():
+    """Each GPU holds its own copy of the array, looked up with that GPU current."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from cuda_transformer_b200 import _lib, amp
+    lib = _lib.load()
+    n = 1 << 18
+    host = _inputs(n, 4, 2048.0).cpu()
+    answers = []
+    for dev in (0, 1):
+        with torch.cuda.device(dev):
+            grads = host.to(f"cuda:{dev}")
+            state = torch.frombuffer(bytearray(bytes(amp.initial_state(2048.0))), dtype=torch.uint8).to(f"cuda:{dev}")
+            workspace = torch.zeros(lib.b200amp_workspace_bytes(), dtype=torch.uint8, device=f"cuda:{dev}")
+            out = torch.zeros(2, dtype=torch.float64, device=f"cuda:{dev}")
+            amp.pass1_f16(grads, n, state, workspace)
+            amp.pass1_f16_static(grads, n, state, out)
+            torch.cuda.synchronize()
+            assert torch.equal(out, workspace[:16].view(torch.float64))
+            answers.append(out.cpu().numpy())
+    assert np.array_equal(answers[0], answers[1])
