@@ -357,7 +357,7 @@ def run_gpu(args) -> dict:
             # it, every rank falls back together to NCCL around the passes (and the line says so)
             try:
                 opt = amp.FusedZero1Optimizer(slots, cfg, eps=1e-8, loss_scale=loss_scale, device=dev,
-                                              mover=args.mover, ce_use=args.ce_use, pieces=args.pieces)
+                                              rs_mover=args.rs_mover, ag_mover=args.ag_mover, pieces=args.pieces)
                 ok = torch.ones(1, device=dev)
             except Exception as e:      # noqa: BLE001
                 opt, ok, fused_note = None, torch.zeros(1, device=dev), f"{type(e).__name__}: {e}"[:200]
@@ -482,10 +482,11 @@ def run_gpu(args) -> dict:
         n_local = opt.n_local
         phases["rs_pass1_nvlink_gbs"] = coll_bytes / (phases["rs_pass1_ms"] * 1e-3) / 1e9
         phases["pass2_ag_nvlink_gbs"] = coll_bytes / (phases["pass2_ag_ms"] * 1e-3) / 1e9
-        if args.mover == "ce":
-            phases["collectives"] = (f"copy engines under the passes ({args.ce_use}, {args.pieces} pieces): peers' "
-                                     "slices pulled into staging / weights pushed by cudaMemcpyAsync while the "
-                                     "kernels run on local memory; ranks ordered by the library's flag words")
+        if args.rs_mover != "sm" or args.ag_mover != "sm":
+            phases["collectives"] = (f"reduce-scatter mover {args.rs_mover}, all-gather mover {args.ag_mover}, "
+                                     f"{args.pieces} pieces (sm: peer loads / stores issued by the fused kernel; "
+                                     "ce_*: cudaMemcpyAsync under kernels that touch local memory only); ranks "
+                                     "ordered by the library's flag words, every wait bounded")
         else:
             phases["collectives"] = ("fused into the passes: plain peer loads (rs_pass1) and peer stores "
                                      "(pass2_ag); ranks ordered by the library's flag words, every wait bounded")
@@ -674,8 +675,7 @@ def run_gpu(args) -> dict:
         bound_peak = link_peak if by_link else peak
         line["roofline"].update({
             "bound": "nvlink" if by_link else "hbm",
-            "kernel": "pass2_f16_kernel + cudaMemcpyAsync" if args.mover == "ce" and "ag" in args.ce_use
-                      else "pass2_ag_f16_kernel",
+            "kernel": "pass2_f16_kernel + cudaMemcpyAsync" if args.ag_mover == "ce" else "pass2_ag_f16_kernel",
             "achieved": achieved, "peak": bound_peak, "frac": achieved / bound_peak,
             "peak_kind": link_kind if by_link else f"{peak_kind} copy bandwidth",
             "floor_ms": {"hbm": t_hbm * 1e3, "nvlink": t_link * 1e3}, "traffic": None,
@@ -798,10 +798,12 @@ def main() -> None:
                     help="N = 1: decay flags from the tensor table in device memory, or as a kernel parameter")
     ap.add_argument("--collectives", choices=["fused", "nccl"], default="fused",
                     help="N > 1: fold reduce-scatter / all-gather into the passes, or call NCCL around them")
-    ap.add_argument("--mover", choices=["sm", "ce"], default="sm",
-                    help="N > 1, fused: peer loads and stores issued by the kernels, or the copy engines")
-    ap.add_argument("--ce-use", choices=["rs", "ag", "rs+ag"], default="rs+ag")
-    ap.add_argument("--pieces", type=int, default=4)
+    ap.add_argument("--rs-mover", choices=["sm", "ce_pull", "ce_push"], default="sm",
+                    help="N > 1, fused: who moves the reduce-scatter's bytes over NVLink (the kernel's peer loads, "
+                         "or the copy engines pulling / pushing)")
+    ap.add_argument("--ag-mover", choices=["sm", "ce"], default="sm",
+                    help="N > 1, fused: who moves the all-gather's bytes (the kernel's peer stores, or the copy engines)")
+    ap.add_argument("--pieces", type=int, default=4, help="pipelining of the copy-engine movers")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))

@@ -58,8 +58,8 @@ class DecayRuns(C.Structure):
     _fields_ = [("first4", C.c_uint * 256), ("nruns", C.c_int), ("flag0", C.c_int)]
 
 
-ZERO1_SYNC_BYTES = 256
-SYNC_SIGNAL, SYNC_WAIT, SYNC_ADVANCE = 1, 2, 4
+ZERO1_SYNC_BYTES = 1024
+SYNC_SIGNAL, SYNC_WAIT, SYNC_ADVANCE, SYNC_STAMP = 1, 2, 4, 8
 PHASE_GRADS, PHASE_PAIRS, PHASE_WEIGHTS = 0, 1, 2
 
 assert C.sizeof(StepState) == 60 and C.sizeof(ScheduleConfig) == 44 and C.sizeof(TensorInfo) == 24
@@ -104,6 +104,8 @@ PROTOTYPES = {
     "b200amp_rs_pass1_f16_sync": (_I, [_P, _I, _I, _P, _LL, _P, _P, _P, C.POINTER(Zero1Sync), _P]),
     "b200amp_finalize_sums_sync": (_I, [_P, _P, _I, _I, C.POINTER(ScheduleConfig), _P, _I, C.POINTER(Zero1Sync), _P]),
     "b200amp_rs_pass1_f16_ce": (_I, [_P, _I, _I, _P, _P, _LL, _I, _P, _P, _P, C.POINTER(Zero1Sync), _P]),
+    "b200amp_rs_push_f16_ce": (_I, [_P, _P, _I, _I, _LL, _I, C.POINTER(Zero1Sync), _P]),
+    "b200amp_rs_pass1_f16_pushed": (_I, [_P, _P, _I, _I, _P, _LL, _I, _P, _P, _P, C.POINTER(Zero1Sync), _P]),
     "b200amp_pass2_ag_f16_ce": (_I, [_P, _P, _P, _P, _P, _I, _I, _LL, _LL, _P, _I, _P, _F, _F, _F, _I, _P]),
     "b200amp_step_f16": (_I, [_P, _P, _P, _P, _P, _LL, _P, _I, _P, _P, C.POINTER(ScheduleConfig), _P, _I,
                               _F, _F, _F, _P]),

@@ -274,6 +274,24 @@ def rs_pass1_f16_ce(grads16_by_rank: Sequence[int], my_rank: int, staging16, red
                                               C.byref(sync) if sync is not None else None, _stream(stream)))
 
 
+def rs_push_f16_ce(grads16, staging_by_rank: Sequence[int], my_rank: int, n: int, pieces: int, sync: Zero1Sync,
+                   stream=None) -> None:
+    """Reduce-scatter by push, sender's side: slice q of this rank's arena into row my_rank of rank
+    q's staging buffer, piece by piece, each piece followed by its flag (copy engines)."""
+    check(_lib.load().b200amp_rs_push_f16_ce(_ptr(grads16), _pointer_array(staging_by_rank), len(staging_by_rank),
+                                             my_rank, n, pieces, C.byref(sync), _stream(stream)))
+
+
+def rs_pass1_f16_pushed(own_slice16, staging16, nranks: int, my_rank: int, reduced16, n: int, pieces: int, st,
+                        workspace, pair_table_by_rank: Sequence[int], sync: Zero1Sync, stream=None) -> None:
+    """Reduce-scatter by push, owner's side: pass 1 over the rank's own slice and the staging rows
+    its peers filled, each piece waiting (bounded) for its flags."""
+    check(_lib.load().b200amp_rs_pass1_f16_pushed(_ptr(own_slice16), _ptr(staging16), nranks, my_rank,
+                                                  _ptr(reduced16), n, pieces, _ptr(st), _ptr(workspace),
+                                                  _pointer_array(pair_table_by_rank), C.byref(sync),
+                                                  _stream(stream)))
+
+
 def pass2_ag_f16_ce(master, m, v, reduced16, weights16_by_rank: Sequence[int], my_rank: int, n: int,
                     arena_offset: int, tensors, ntensors: int, st, beta1: float, beta2: float, eps: float,
                     pieces: int, stream=None) -> None:
@@ -642,7 +660,7 @@ class FusedZero1Optimizer(ShardedAmpOptimizer):
     and the ordering between the ranks done by the library's own flag words.
 
     The fp16 gradient arena, the fp16 weight arena, the table of {sum, flag} pairs and one
-    256-byte block of flag words are allocated as symmetric memory
+    1 KB block of flag words are allocated as symmetric memory
     (torch.distributed._symmetric_memory, used for the allocation and the mapping only): every
     rank's buffers are mapped into every process, so a kernel reads a peer's gradients and writes a
     peer's weights with ordinary loads and stores over NVLink. Multicast binding is switched off
@@ -658,9 +676,12 @@ class FusedZero1Optimizer(ShardedAmpOptimizer):
         barrier             announces "my weights have landed", waits for every rank's, advances
                             the step counter that lives in the flag block
 
-    mover="ce" moves the NVLink bytes with the copy engines instead (b200amp_rs_pass1_f16_ce,
-    b200amp_pass2_ag_f16_ce; `ce_use` picks the phases, `pieces` the pipelining); the results are
-    the same bits.
+    The NVLink bytes can be moved by the copy engines instead, phase by phase; the results are
+    the same bits. rs_mover: "sm" (peer loads of the kernel), "ce_pull" (peers' slices pulled into
+    local staging, b200amp_rs_pass1_f16_ce) or "ce_push" (every rank writes its slices into the
+    owners' staging rows, b200amp_rs_push_f16_ce + b200amp_rs_pass1_f16_pushed). ag_mover: "sm"
+    (peer stores of the kernel) or "ce" (pieces pushed under pass 2, b200amp_pass2_ag_f16_ce).
+    `pieces` sets the pipelining of the copy-engine forms.
 
     Every wait is bounded (about a second, `wait_limit` polls). A rank that never shows up makes
     the others' kernels return without applying the step; read_state() then raises
@@ -669,22 +690,22 @@ class FusedZero1Optimizer(ShardedAmpOptimizer):
     flag are taken on exactly the stored averaged values.
     """
 
-    PHASE_NAMES = ("gradients ready", "pairs written", "weights written")
+    PHASE_NAMES = ("gradients ready", "pairs written", "weights written", "a pushed piece of gradients")
 
     def __init__(self, slots: List[ParamSlot], cfg: ScheduleConfig, eps: float = 1e-8,
                  loss_scale: float = 65536.0, history_len: int = 256, device=None, group=None,
-                 mover: str = "sm", ce_use: str = "rs+ag", pieces: int = 4, wait_limit: int = 0):
+                 rs_mover: str = "sm", ag_mover: str = "sm", pieces: int = 4, wait_limit: int = 0):
         import os
         import torch.distributed as dist
         # the kernels use plain peer loads and stores: do not bind the arenas to an NVLink multicast
         # object (a rank that dies while bound to one can fault its peers' GPUs)
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
-        if mover not in ("sm", "ce"):
-            raise ValueError(f"mover = {mover!r}: expected 'sm' or 'ce'")
-        if ce_use not in ("rs", "ag", "rs+ag"):
-            raise ValueError(f"ce_use = {ce_use!r}: expected 'rs', 'ag' or 'rs+ag'")
-        self.mover, self.ce_use, self.pieces = mover, ce_use, pieces
+        if rs_mover not in ("sm", "ce_pull", "ce_push"):
+            raise ValueError(f"rs_mover = {rs_mover!r}: expected 'sm', 'ce_pull' or 'ce_push'")
+        if ag_mover not in ("sm", "ce"):
+            raise ValueError(f"ag_mover = {ag_mover!r}: expected 'sm' or 'ce'")
+        self.rs_mover, self.ag_mover, self.pieces = rs_mover, ag_mover, pieces
         self._symm_mem = symm_mem
         self._symm_group = group if group is not None else dist.group.WORLD
         self._handles = {}
@@ -702,12 +723,26 @@ class FusedZero1Optimizer(ShardedAmpOptimizer):
             self._weight_ptrs = [int(p) + shard_bytes for p in self._handles["weights16"].buffer_ptrs]
             self._pair_ptrs = [int(p) for p in self._handles["pairs"].buffer_ptrs]
             self.sync = make_sync([int(p) for p in self._handles["sync_block"].buffer_ptrs], wait_limit)
-            self.staging = None
-            if mover == "ce" and "rs" in ce_use and self.world > 1:
-                self.staging = torch.empty((self.world - 1) * self.n_local, dtype=torch.float16, device=self.device)
+            self.staging = None             # ce_pull: (world - 1) slices, local, allocated on first use
+            self.push_rows = None           # ce_push: world rows of one slice, mapped by every rank (below)
+            self._push_ptrs = None
             torch.cuda.current_stream().synchronize()
+        if rs_mover == "ce_push":
+            self.enable_push()
         # once, on the host: every rank's block is zeroed and mapped before any rank announces anything
         dist.barrier(group=self._symm_group)
+
+    def enable_push(self) -> None:
+        """Allocates and maps the staging rows the ce_push reduce-scatter writes into. Collective:
+        every rank calls it."""
+        if self.push_rows is not None or self.world == 1:
+            return
+        with torch.cuda.device(self.device):
+            self.push_rows = self._symm_mem.empty(self.world * self.n_local, dtype=torch.float16, device=self.device)
+            self.push_rows.zero_()
+            torch.cuda.current_stream().synchronize()
+            self._handles["push_rows"] = self._symm_mem.rendezvous(self.push_rows, self._symm_group)
+            self._push_ptrs = [int(p) for p in self._handles["push_rows"].buffer_ptrs]
 
     def _alloc_arena16(self, name: str) -> torch.Tensor:
         with torch.cuda.device(self.device):
@@ -716,9 +751,18 @@ class FusedZero1Optimizer(ShardedAmpOptimizer):
             return t
 
     def fused_pass1(self) -> None:
-        if self.mover == "ce" and "rs" in self.ce_use and self.world > 1:
+        if self.world > 1 and self.rs_mover == "ce_pull":
+            if self.staging is None:
+                self.staging = torch.empty((self.world - 1) * self.n_local, dtype=torch.float16, device=self.device)
             rs_pass1_f16_ce(self._grad_ptrs, self.rank, self.staging, self.grad_shard, self.n_local, self.pieces,
                             self.state, self.workspace, self._pair_ptrs, self.sync)
+        elif self.world > 1 and self.rs_mover == "ce_push":
+            if self._push_ptrs is None:
+                raise RuntimeError("rs_mover 'ce_push' needs enable_push() on every rank first")
+            rs_push_f16_ce(self.grads16, self._push_ptrs, self.rank, self.n_local, self.pieces, self.sync)
+            rs_pass1_f16_pushed(self.grads16[self.begin:self.end], self.push_rows, self.world, self.rank,
+                                self.grad_shard, self.n_local, self.pieces, self.state, self.workspace,
+                                self._pair_ptrs, self.sync)
         else:
             rs_pass1_f16_sync(self._grad_ptrs, self.rank, self.grad_shard, self.n_local, self.state, self.workspace,
                               self._pair_ptrs, self.sync)
@@ -728,7 +772,7 @@ class FusedZero1Optimizer(ShardedAmpOptimizer):
                            self.history_len)
 
     def fused_pass2(self) -> None:
-        if self.mover == "ce" and "ag" in self.ce_use and self.world > 1:
+        if self.world > 1 and self.ag_mover == "ce":
             pass2_ag_f16_ce(self.master, self.m, self.v, self.grad_shard, self._weight_ptrs, self.rank,
                             self.n_local, self.begin, self.tensors, self.ntensors, self.state, self.beta1,
                             self.beta2, self.eps, self.pieces)
@@ -760,7 +804,7 @@ class FusedZero1Optimizer(ShardedAmpOptimizer):
         _, error = self.sync_status()
         if error != 0:
             phase, missing = (error & 0xFF) - 1, error >> 8
-            what = self.PHASE_NAMES[phase] if 0 <= phase < 3 else f"phase {phase}"
+            what = self.PHASE_NAMES[phase] if 0 <= phase < 4 else f"phase {phase}"
             raise RankWaitError(_lib.ERR_CUDA, f"rank {self.rank} gave up waiting for '{what}' of rank {missing}; "
                                 "the step was not applied")
         return st

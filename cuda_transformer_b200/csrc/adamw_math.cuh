@@ -245,4 +245,66 @@ __device__ __forceinline__ void update_group(float *__restrict__ master, float *
     emit(j, out);
 }
 
+// ---------------------------------------------------------------- the sweep of pass 2
+
+// How many trips (groups i, i + stride, i + 2 stride, ...) a thread can take from group i on with
+// every group wholly inside the cursor's run and inside the range: 0 when group i itself is not.
+__device__ __forceinline__ int trips_inside(const Cursor &c, long long at, int i, int groups, int stride)
+{
+    if (i >= groups || at + 8 > c.next)
+    {
+        return 0;
+    }
+    const int by_end = (groups - 1 - i) / stride + 1;
+    const long long room = c.next - 8 - at;             // elements between this group and the last one that fits
+    if (room >= (static_cast<long long>(by_end) * stride) * 8)
+    {
+        return by_end;
+    }
+    const unsigned int room_groups = static_cast<unsigned int>(room >> 3);  // < by_end * stride < 2^31
+    return static_cast<int>(room_groups / static_cast<unsigned int>(stride)) + 1;
+}
+
+// One thread's share of the range: groups first, first + stride, ... < groups. The sweep
+// alternates between ONE trip that looks its decay factors up (the cursor moves, a group may
+// straddle two runs) and a stretch of trips that need no lookup at all: as many as every lane of
+// the warp can take inside its current run, agreed on with one warp-wide minimum so that the
+// lanes stay in step. The stretch's loop is the plain update with a constant factor. Every lane
+// of every warp must call this (lanes with nothing left keep the warp-wide votes company).
+template <int ST, class Table, class EmitFn>
+__device__ __forceinline__ void sweep_groups(float *__restrict__ master, float *__restrict__ m, float *__restrict__ v,
+                                             const uint4 *__restrict__ g16, const Table &tab, int nruns,
+                                             long long arena_offset, int groups, int first, int stride,
+                                             float wd_decay, const StepFactors &f, EmitFn emit)
+{
+    constexpr unsigned FULL = 0xffffffffu;
+    int i = first;
+    Cursor cur = cursor_seek(tab, nruns, arena_offset + static_cast<long long>(i) * 8, wd_decay);
+    for (;;)
+    {
+        const bool active = i < groups;
+        if (!__any_sync(FULL, active))
+        {
+            break;
+        }
+        if (active)
+        {
+            const long long at = arena_offset + static_cast<long long>(i) * 8;
+            update_group<ST>(
+                master, m, v, g16, i,
+                [&](float &d_lo, float &d_hi) { group_decay(cur, tab, nruns, at, wd_decay, d_lo, d_hi); }, emit, f);
+            i += stride;
+        }
+        const int mine = trips_inside(cur, arena_offset + static_cast<long long>(i) * 8, i, groups, stride);
+        const int fast = __reduce_min_sync(FULL, mine);
+        const float factor = cur.factor;
+        for (int t = 0; t < fast; t++)
+        {
+            update_group<ST>(
+                master, m, v, g16, i, [&](float &d_lo, float &d_hi) { d_lo = factor; d_hi = factor; }, emit, f);
+            i += stride;
+        }
+    }
+}
+
 } // namespace b200amp

@@ -35,8 +35,8 @@ namespace b200amp
 // ---------------------------------------------------------------- registers-only kernel
 
 // The whole grid sweeps the arena together: group i of a sweep belongs to thread i mod
-// (grid * THREADS). A thread's positions only grow, so it walks the tensor table once; while
-// its groups stay inside one tensor the decay lookup is a single compare (group_decay).
+// (grid * THREADS). A thread's positions only grow, so it walks the tensor table once, and
+// between two run boundaries its warp runs trips with no decay lookup at all (sweep_groups).
 template <int THREADS, int ST>
 __global__ void __launch_bounds__(THREADS)
     pass2_f16_kernel(float *__restrict__ master, float *__restrict__ m, float *__restrict__ v,
@@ -57,26 +57,14 @@ __global__ void __launch_bounds__(THREADS)
     // multiply-add makes each address, and the loop counter is a single register
     const int groups = static_cast<int>(n8);
     const int stride = static_cast<int>(gridDim.x) * THREADS;
-    int i = static_cast<int>(blockIdx.x) * THREADS + static_cast<int>(threadIdx.x);
-    if (i >= groups)
-    {
-        return;
-    }
-    Cursor cur = cursor_seek(tab, nruns, arena_offset + static_cast<long long>(i) * 8, wd_decay);
-    for (; i < groups; i += stride)
-    {
-        const long long at = arena_offset + static_cast<long long>(i) * 8;
-        update_group<ST>(
-            master, m, v, g16, i,
-            [&](float &d_lo, float &d_hi) { group_decay(cur, tab, nruns, at, wd_decay, d_lo, d_hi); },
-            [&](int j, const uint4 &half8) {
-                if (w16 != nullptr)
-                {
-                    store_h8<ST>(w16 + j, half8);
-                }
-            },
-            f);
-    }
+    const int first = static_cast<int>(blockIdx.x) * THREADS + static_cast<int>(threadIdx.x);
+    sweep_groups<ST>(master, m, v, g16, tab, nruns, arena_offset, groups, first, stride, wd_decay, f,
+                     [&](int j, const uint4 &half8) {
+                         if (w16 != nullptr)
+                         {
+                             store_h8<ST>(w16 + j, half8);
+                         }
+                     });
 }
 
 // The same sweep with the decay runs as a kernel parameter (b200amp_decay_runs, at most
@@ -98,26 +86,14 @@ __global__ void __launch_bounds__(THREADS)
     const int nruns = runs.nruns;
     const int groups = static_cast<int>(n8);
     const int stride = static_cast<int>(gridDim.x) * THREADS;
-    int i = static_cast<int>(blockIdx.x) * THREADS + static_cast<int>(threadIdx.x);
-    if (i >= groups)
-    {
-        return;
-    }
-    Cursor cur = cursor_seek(runs, nruns, arena_offset + static_cast<long long>(i) * 8, wd_decay);
-    for (; i < groups; i += stride)
-    {
-        const long long at = arena_offset + static_cast<long long>(i) * 8;
-        update_group<ST>(
-            master, m, v, g16, i,
-            [&](float &d_lo, float &d_hi) { group_decay(cur, runs, nruns, at, wd_decay, d_lo, d_hi); },
-            [&](int j, const uint4 &half8) {
-                if (w16 != nullptr)
-                {
-                    store_h8<ST>(w16 + j, half8);
-                }
-            },
-            f);
-    }
+    const int first = static_cast<int>(blockIdx.x) * THREADS + static_cast<int>(threadIdx.x);
+    sweep_groups<ST>(master, m, v, g16, runs, nruns, arena_offset, groups, first, stride, wd_decay, f,
+                     [&](int j, const uint4 &half8) {
+                         if (w16 != nullptr)
+                         {
+                             store_h8<ST>(w16 + j, half8);
+                         }
+                     });
 }
 
 // ---------------------------------------------------------------- shared-memory staged kernel

@@ -91,7 +91,9 @@ constexpr int RS_UNROLL = B200AMP_RS_UNROLL;    // vectors per thread per trip: 
 // stream, so they are complete before that one starts).
 // sy: the ranks' flag blocks (off when block[0] is null). SYNC_ENTER_GRADS: every CTA announces
 // this rank's gradients and waits for every rank's before it loads anything; a CTA whose wait
-// gave up does no work. SYNC_SIGNAL_PAIRS: the last CTA announces the pairs it has written.
+// gave up does no work. SYNC_WAIT_PIECE: every CTA waits until piece sy.piece of every peer's pushed
+// gradients has landed in this rank's staging rows. SYNC_SIGNAL_PAIRS: the last CTA announces the
+// pairs it has written.
 template <int R>
 __global__ void __launch_bounds__(P1_THREADS)
     rs_pass1_f16_kernel(ConstPtrs src, uint4 *__restrict__ reduced, long long n8, const b200amp_step_state *st,
@@ -107,7 +109,8 @@ __global__ void __launch_bounds__(P1_THREADS)
         bool ok = true;
         if (threadIdx.x < R)
         {
-            ok = (sy.mode & SYNC_ENTER_GRADS) ? sync_exchange(sy, SYNC_PHASE_GRADS, threadIdx.x, true, true)
+            ok = (sy.mode & SYNC_ENTER_GRADS)  ? sync_exchange(sy, SYNC_PHASE_GRADS, threadIdx.x, true, true)
+                 : (sy.mode & SYNC_WAIT_PIECE) ? sync_await_piece(sy, threadIdx.x)
                                                : !sync_failed(sy);
         }
         alive = __syncthreads_and(ok) != 0;
@@ -252,7 +255,8 @@ __global__ void finalize_sums_sync_kernel(b200amp_step_state *st, const double *
 }
 
 // One warp. what & 1: announce `phase` of the step in flight to every rank; & 2: wait for it from
-// every rank; & 4: the step is over on this rank, advance its counter (only if nothing gave up).
+// every rank; & 4: the step is over on this rank, advance its counter (only if nothing gave up);
+// & 8: write the step in flight into the STAMP word (the source of the copy engines' piece flags).
 __global__ void zero1_barrier_kernel(SyncArgs sy, int nranks, int phase, int what)
 {
     bool ok = true;
@@ -260,7 +264,11 @@ __global__ void zero1_barrier_kernel(SyncArgs sy, int nranks, int phase, int wha
     if (static_cast<int>(threadIdx.x) < nranks)
     {
         e = sync_epoch(sy);
-        ok = sync_exchange(sy, phase, threadIdx.x, (what & 1) != 0, (what & 2) != 0);
+        if (threadIdx.x == 0 && (what & 8))
+        {
+            sync_local(sy)[SYNC_STAMP] = e;
+        }
+        ok = (what & 3) ? sync_exchange(sy, phase, threadIdx.x, (what & 1) != 0, (what & 2) != 0) : !sync_failed(sy);
     }
     ok = __all_sync(0xffffffffu, ok);
     if (threadIdx.x == 0 && ok && (what & 4))
@@ -291,27 +299,15 @@ __global__ void __launch_bounds__(256)
     // 32-bit group indices, as pass2_f16_kernel (the launcher refuses longer ranges)
     const int groups = static_cast<int>(n8);
     const int stride = static_cast<int>(gridDim.x) * THREADS;
-    int i = static_cast<int>(blockIdx.x) * THREADS + static_cast<int>(threadIdx.x);
-    if (i >= groups)
-    {
-        return;
-    }
-    Cursor cur = cursor_seek(tab, nruns, arena_offset + static_cast<long long>(i) * 8, wd_decay);
-    for (; i < groups; i += stride)
-    {
-        const long long at = arena_offset + static_cast<long long>(i) * 8;
-        update_group<1>(
-            master, m, v, g16, i,
-            [&](float &d_lo, float &d_hi) { group_decay(cur, tab, nruns, at, wd_decay, d_lo, d_hi); },
-            [&](int j, const uint4 &half8) {
+    const int first = static_cast<int>(blockIdx.x) * THREADS + static_cast<int>(threadIdx.x);
+    sweep_groups<1>(master, m, v, g16, tab, nruns, arena_offset, groups, first, stride, wd_decay, f,
+                    [&](int j, const uint4 &half8) {
 #pragma unroll
-                for (int r = 0; r < R; r++)
-                {
-                    store_h8<B200AMP_AG_STORE_HINT>(static_cast<uint4 *>(dst.p[r]) + j, half8);
-                }
-            },
-            f);
-    }
+                        for (int r = 0; r < R; r++)
+                        {
+                            store_h8<B200AMP_AG_STORE_HINT>(static_cast<uint4 *>(dst.p[r]) + j, half8);
+                        }
+                    });
 }
 
 static int check_ranks(int nranks, int my_rank, const char *who)
@@ -328,11 +324,12 @@ using namespace b200amp;
 
 // The flag blocks of a b200amp_zero1_sync as kernel arguments. sync == null: off.
 static int sync_args(const b200amp_zero1_sync *sync, int nranks, int my_rank, int mode, const char *who,
-                     SyncArgs *out)
+                     SyncArgs *out, int piece = 0)
 {
     SyncArgs a = {};
     a.my_rank = my_rank;
     a.mode = mode;
+    a.piece = piece;
     if (sync != nullptr)
     {
         for (int r = 0; r < nranks; r++)
@@ -351,7 +348,7 @@ static int sync_args(const b200amp_zero1_sync *sync, int nranks, int my_rank, in
 static int rs_pass1_launch(const void *const *grads16_by_rank, int nranks, int my_rank, void *reduced16, long long n,
                            int vblock_first, int vblock_count, int last_part, const b200amp_step_state *st,
                            void *workspace, double *const *pair_table_by_rank, const b200amp_zero1_sync *sync,
-                           int sync_mode, b200amp_stream s)
+                           int sync_mode, b200amp_stream s, int piece = 0)
 {
     int rc = check_ranks(nranks, my_rank, "rs_pass1");
     if (rc != B200AMP_OK)
@@ -374,7 +371,7 @@ static int rs_pass1_launch(const void *const *grads16_by_rank, int nranks, int m
         B200AMP_REQUIRE(aligned(tables.p[r], 8), "rs_pass1: pair table of rank %d is not 8-byte aligned", r);
     }
     SyncArgs sy;
-    rc = sync_args(sync, nranks, my_rank, sync_mode, "rs_pass1", &sy);
+    rc = sync_args(sync, nranks, my_rank, sync_mode, "rs_pass1", &sy, piece);
     if (rc != B200AMP_OK)
     {
         return rc;
@@ -503,8 +500,8 @@ extern "C" B200AMP_API int b200amp_zero1_barrier(const b200amp_zero1_sync *sync,
     }
     B200AMP_REQUIRE(sync != nullptr, "zero1_barrier: sync is null");
     B200AMP_REQUIRE(phase >= 0 && phase <= SYNC_PHASE_WEIGHTS, "zero1_barrier: phase = %d, must be 0, 1 or 2", phase);
-    B200AMP_REQUIRE(what > 0 && what < 8, "zero1_barrier: what = %d, must be a combination of SIGNAL, WAIT and "
-                                          "ADVANCE", what);
+    B200AMP_REQUIRE(what > 0 && what < 16, "zero1_barrier: what = %d, must be a combination of SIGNAL, WAIT, "
+                                           "ADVANCE and STAMP", what);
     SyncArgs sy;
     rc = sync_args(sync, nranks, my_rank, 0, "zero1_barrier", &sy);
     if (rc != B200AMP_OK)
@@ -772,6 +769,117 @@ extern "C" B200AMP_API int b200amp_rs_pass1_f16_ce(const void *const *grads16_by
         const bool last = i == pieces - 1;
         rc = rs_pass1_launch(local_src, nranks, my_rank, reduced16, n, vb0, vb1 - vb0, last ? 1 : 0, st, workspace,
                              pair_table_by_rank, sync, last ? SYNC_SIGNAL_PAIRS : 0, s);
+        if (rc != B200AMP_OK)
+        {
+            return rc;
+        }
+    }
+    return B200AMP_OK;
+}
+
+// Reduce-scatter by PUSH: writes travel better than reads on links that are busy in both
+// directions (a read's request packets share the direction the peer's data uses). Every rank
+// copies slice q of its own gradient arena into row my_rank of rank q's staging buffer, piece by
+// piece, each piece followed on the same copy stream by a 4-byte copy of this rank's STAMP word
+// (the step in flight) into word PIECE[p][my_rank] of rank q's flag block. The owner's reduction of
+// piece p (b200amp_rs_pass1_f16_pushed) waits for those words and then reads local memory only.
+extern "C" B200AMP_API int b200amp_rs_push_f16_ce(const void *grads16, void *const *staging_by_rank, int nranks,
+                                                  int my_rank, long long n, int pieces,
+                                                  const b200amp_zero1_sync *sync, b200amp_stream s)
+{
+    int rc = check_ranks(nranks, my_rank, "rs_push_ce");
+    if (rc != B200AMP_OK)
+    {
+        return rc;
+    }
+    B200AMP_REQUIRE(grads16 != nullptr && staging_by_rank != nullptr && sync != nullptr, "rs_push_ce: null pointer");
+    B200AMP_REQUIRE(n > 0 && n % 8 == 0, "rs_push_ce: n = %lld must be a positive multiple of 8", n);
+    for (int r = 0; r < nranks; r++)
+    {
+        B200AMP_REQUIRE(staging_by_rank[r] != nullptr && sync->block_by_rank[r] != nullptr,
+                        "rs_push_ce: staging buffer or flag block of rank %d is null", r);
+    }
+    CopyLanes *lanes = nullptr;
+    rc = copy_lanes(&lanes);
+    if (rc != B200AMP_OK)
+    {
+        return rc;
+    }
+    const int nlanes = lane_count(nranks);
+    const P1Partition part = p1_partition(n / 8);
+    const long long per = part.vec_per_vblock * 8;
+    pieces = clamp_pieces(pieces, part.vblocks);
+    pieces = pieces > SYNC_MAX_PIECES ? SYNC_MAX_PIECES : pieces;
+    cudaStream_t stream = as_stream(s);
+    // the step in flight into the STAMP word, then the copies may start
+    rc = b200amp_zero1_barrier(sync, nranks, my_rank, 0, 8, s);
+    if (rc != B200AMP_OK)
+    {
+        return rc;
+    }
+    B200AMP_CUDA(cudaEventRecord(lanes->start, stream));
+    const char *mine = static_cast<const char *>(grads16);
+    const unsigned int *stamp = static_cast<const unsigned int *>(sync->block_by_rank[my_rank]) + SYNC_STAMP;
+    bool forked[MAX_LANES] = {};
+    int turn = 0;
+    for (int i = 0; i < pieces; i++)
+    {
+        const int vb0 = static_cast<int>(static_cast<long long>(part.vblocks) * i / pieces);
+        const int vb1 = static_cast<int>(static_cast<long long>(part.vblocks) * (i + 1) / pieces);
+        const long long e0 = vb0 * per;
+        const long long e1 = vb1 * per < n ? vb1 * per : n;
+        for (int k = 1; k < nranks; k++)
+        {
+            const int peer = (my_rank + k) % nranks;            // every rank writes to a different peer at a time
+            const int lane = turn++ % nlanes;
+            if (!forked[lane])
+            {
+                B200AMP_CUDA(cudaStreamWaitEvent(lanes->stream[lane], lanes->start, 0));
+                forked[lane] = true;
+            }
+            char *row = static_cast<char *>(staging_by_rank[peer]) + static_cast<size_t>(my_rank) * n * 2;
+            B200AMP_CUDA(cudaMemcpyAsync(row + e0 * 2, mine + (static_cast<size_t>(peer) * n + e0) * 2,
+                                         static_cast<size_t>(e1 - e0) * 2, cudaMemcpyDefault, lanes->stream[lane]));
+            unsigned int *flag = static_cast<unsigned int *>(sync->block_by_rank[peer]) + SYNC_PIECE +
+                                 i * MAX_RANKS + my_rank;
+            B200AMP_CUDA(cudaMemcpyAsync(flag, stamp, sizeof(unsigned int), cudaMemcpyDefault, lanes->stream[lane]));
+        }
+    }
+    return B200AMP_OK;
+}
+
+// The owner's side of the pushed reduce-scatter: pass 1 over R local rows (its own slice of its
+// own arena and the R - 1 staging rows the peers filled), in the same pieces, each launch waiting
+// (bounded) for its piece of every peer. pieces must be what the peers pushed with. The last
+// piece writes the pairs and announces them.
+extern "C" B200AMP_API int b200amp_rs_pass1_f16_pushed(const void *own_slice16, const void *staging16, int nranks,
+                                                       int my_rank, void *reduced16, long long n, int pieces,
+                                                       const b200amp_step_state *st, void *workspace,
+                                                       double *const *pair_table_by_rank,
+                                                       const b200amp_zero1_sync *sync, b200amp_stream s)
+{
+    int rc = check_ranks(nranks, my_rank, "rs_pass1_pushed");
+    if (rc != B200AMP_OK)
+    {
+        return rc;
+    }
+    B200AMP_REQUIRE(own_slice16 != nullptr && staging16 != nullptr && sync != nullptr && n > 0 && n % 8 == 0,
+                    "rs_pass1_pushed: null pointer or n = %lld not a positive multiple of 8", n);
+    const P1Partition part = p1_partition(n / 8);
+    pieces = clamp_pieces(pieces, part.vblocks);
+    pieces = pieces > SYNC_MAX_PIECES ? SYNC_MAX_PIECES : pieces;
+    const void *src[MAX_RANKS] = {};
+    for (int r = 0; r < nranks; r++)
+    {
+        src[r] = r == my_rank ? own_slice16 : static_cast<const char *>(staging16) + static_cast<size_t>(r) * n * 2;
+    }
+    for (int i = 0; i < pieces; i++)
+    {
+        const int vb0 = static_cast<int>(static_cast<long long>(part.vblocks) * i / pieces);
+        const int vb1 = static_cast<int>(static_cast<long long>(part.vblocks) * (i + 1) / pieces);
+        const bool last = i == pieces - 1;
+        rc = rs_pass1_launch(src, nranks, my_rank, reduced16, n, vb0, vb1 - vb0, last ? 1 : 0, st, workspace,
+                             pair_table_by_rank, sync, SYNC_WAIT_PIECE | (last ? SYNC_SIGNAL_PAIRS : 0), s, i);
         if (rc != B200AMP_OK)
         {
             return rc;

@@ -28,17 +28,24 @@ constexpr int SYNC_PHASE_PAIRS = 1;     // [8..15]  rank q has written its {sum,
 constexpr int SYNC_PHASE_WEIGHTS = 2;   // [16..23] rank q's fp16 weights have landed in every arena
 constexpr int SYNC_EPOCH = 24;          // steps this rank has completed (only the owner writes it)
 constexpr int SYNC_ERROR = 25;          // 0, or what a wait gave up on: (phase + 1) | missing rank << 8
+constexpr int SYNC_STAMP = 26;          // the step in flight, written at its start: what a copy engine copies into
+                                        // a peer's PIECE word after the data it announces
+constexpr int SYNC_PIECE = 32;          // [32 + 8 p + q] piece p of rank q's gradients has landed in my staging rows
+constexpr int SYNC_MAX_PIECES = 16;
+constexpr int SYNC_PHASE_PIECE = 3;     // phase number recorded when a wait for a piece gives up
 constexpr unsigned SYNC_DEFAULT_LIMIT = 1u << 21;   // polls of one wait: about a second
 
 // what a launch does with the block
 constexpr int SYNC_ENTER_GRADS = 1;     // prologue: announce and await "gradients ready" (rs_pass1)
 constexpr int SYNC_SIGNAL_PAIRS = 2;    // epilogue of the last CTA: announce "pairs written" (rs_pass1)
+constexpr int SYNC_WAIT_PIECE = 4;      // prologue: await piece `piece` of every peer's pushed gradients
 
 struct SyncArgs
 {
     unsigned int *block[MAX_RANKS];     // block[r]: rank r's block as mapped in this process; block[0] == null: off
     int my_rank;
     int mode;
+    int piece;
     unsigned int limit;
 };
 
@@ -101,12 +108,12 @@ __device__ __forceinline__ void sync_signal(const SyncArgs &sy, int phase, int t
     sync_store_release(sy.block[to_rank] + phase * MAX_RANKS + sy.my_rank, e);
 }
 
-// Polls word [phase][from_rank] of the own block until it has reached e. False when the limit
-// ran out or another thread of this GPU has already given up. The comparison is on the signed
-// difference, so the counter may wrap.
-__device__ __forceinline__ bool sync_wait(const SyncArgs &sy, int phase, int from_rank, unsigned int e)
+// Polls one word of the own block until it has reached e. False when the limit ran out or
+// another thread of this GPU has already given up. The comparison is on the signed difference,
+// so the counter may wrap.
+__device__ __forceinline__ bool sync_wait_word(const SyncArgs &sy, int index, unsigned int e)
 {
-    const unsigned int *word = sync_local(sy) + phase * MAX_RANKS + from_rank;
+    const unsigned int *word = sync_local(sy) + index;
     const unsigned int limit = sy.limit != 0 ? sy.limit : SYNC_DEFAULT_LIMIT;
     for (unsigned int tries = 0; tries < limit; tries++)
     {
@@ -124,6 +131,30 @@ __device__ __forceinline__ bool sync_wait(const SyncArgs &sy, int phase, int fro
         }
     }
     return false;
+}
+
+__device__ __forceinline__ bool sync_wait(const SyncArgs &sy, int phase, int from_rank, unsigned int e)
+{
+    return sync_wait_word(sy, phase * MAX_RANKS + from_rank, e);
+}
+
+// Thread q: await piece sy.piece of rank q's pushed gradients (nothing to await from itself).
+__device__ __forceinline__ bool sync_await_piece(const SyncArgs &sy, int q)
+{
+    if (sync_failed(sy))
+    {
+        return false;
+    }
+    if (q == sy.my_rank)
+    {
+        return true;
+    }
+    if (!sync_wait_word(sy, SYNC_PIECE + sy.piece * MAX_RANKS + q, sync_epoch(sy)))
+    {
+        sync_give_up(sy, SYNC_PHASE_PIECE, q);
+        return false;
+    }
+    return true;
 }
 
 // Thread q < nranks of the calling warp/CTA: announce `phase` to rank q (if signal) and await it

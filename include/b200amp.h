@@ -320,7 +320,7 @@ B200AMP_API int b200amp_pass2_ag_f16(float *master, float *m, float *v, const vo
  * changes nothing, and the step counter is not advanced. Nothing traps or spins for ever. After
  * a reported give-up the optimizer's state is not to be trusted: restore a checkpoint, zero
  * every rank's block and workspace again, and go on. */
-#define B200AMP_ZERO1_SYNC_BYTES 256
+#define B200AMP_ZERO1_SYNC_BYTES 1024
 typedef struct b200amp_zero1_sync
 {
     void *block_by_rank[8];     /* block_by_rank[r]: rank r's block, a device pointer of the calling process */
@@ -330,7 +330,8 @@ enum
 {
     B200AMP_SYNC_SIGNAL = 1,    /* announce the phase to every rank */
     B200AMP_SYNC_WAIT = 2,      /* wait for every rank's announcement of the phase */
-    B200AMP_SYNC_ADVANCE = 4    /* the step is over on this rank: advance its step counter */
+    B200AMP_SYNC_ADVANCE = 4,   /* the step is over on this rank: advance its step counter */
+    B200AMP_SYNC_STAMP = 8      /* record the step in flight where the copy engines read it (b200amp_rs_push_f16_ce) */
 };
 B200AMP_API int b200amp_zero1_sync_init(void *block, b200amp_stream s);
 /* Synchronous read of a rank's own block: steps completed, and the error word (0 = none). */
@@ -376,6 +377,22 @@ B200AMP_API int b200amp_pass2_ag_f16_ce(float *master, float *m, float *v, const
                                         long long arena_offset, const b200amp_tensor_info *tensors, int ntensors,
                                         const b200amp_step_state *st, float beta1, float beta2, float eps, int pieces,
                                         b200amp_stream s);
+/* Reduce-scatter by push, in two calls per rank. Writes use a link that is busy in both directions
+ * better than reads do, so here every rank WRITES: b200amp_rs_push_f16_ce copies slice q of this
+ * rank's gradient arena (grads16: the start of the arena; slices of n elements) into row my_rank of
+ * rank q's staging buffer (staging_by_rank[q]: nranks rows of n fp16 values, mapped in this
+ * process), in `pieces` pieces (at most 16), each followed on the same copy stream by a 4-byte
+ * copy of the step number into rank q's flag block. b200amp_rs_pass1_f16_pushed then reduces the
+ * owner's rows piece by piece (own_slice16: this rank's slice in its own arena; staging16: its own
+ * staging buffer), each launch waiting, bounded, for its piece of every peer; the last piece
+ * writes the pairs and announces phase 1. No phase-0 exchange is needed. Same bits as
+ * b200amp_rs_pass1_f16. The gradient arena may be overwritten once the step's finalize has run. */
+B200AMP_API int b200amp_rs_push_f16_ce(const void *grads16, void *const *staging_by_rank, int nranks, int my_rank,
+                                       long long n, int pieces, const b200amp_zero1_sync *sync, b200amp_stream s);
+B200AMP_API int b200amp_rs_pass1_f16_pushed(const void *own_slice16, const void *staging16, int nranks, int my_rank,
+                                            void *reduced16, long long n, int pieces, const b200amp_step_state *st,
+                                            void *workspace, double *const *pair_table_by_rank,
+                                            const b200amp_zero1_sync *sync, b200amp_stream s);
 /* cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, s): a copy-engine transfer between any two
  * device pointers of the calling process, a peer's mapped memory included. */
 B200AMP_API int b200amp_copy_async(void *dst, const void *src, long long bytes, b200amp_stream s);

@@ -192,12 +192,23 @@ def _self_ordered_step(run, arenas, world, per, cfg, form="sm", pieces=3, limit=
     bptrs = [b.data_ptr() for b in run["blocks"]]
     sync = amp.make_sync(bptrs, limit)
     tptrs = [t.data_ptr() for t in run["tables"]]
-    for r in range(world):
-        amp.zero1_barrier(sync, world, r, _lib.PHASE_GRADS, _lib.SYNC_SIGNAL)
+    if form == "push":
+        # every emulated rank pushes first (copies and piece flags), then every owner reduces
+        rows = run.setdefault("push_rows", [torch.full((world * per,), 55.0, dtype=torch.float16, device="cuda")
+                                            for _ in range(world)])
+        for r in range(world):
+            amp.rs_push_f16_ce(arenas[r], [x.data_ptr() for x in rows], r, per, pieces, sync)
+        torch.cuda.synchronize()                # the lanes' copies have landed; a real owner's kernels wait instead
+    else:
+        for r in range(world):
+            amp.zero1_barrier(sync, world, r, _lib.PHASE_GRADS, _lib.SYNC_SIGNAL)
     for r, g in enumerate(run["ranks"]):
         src = [a.data_ptr() + 2 * r * per for a in arenas]
         if form == "sm":
             amp.rs_pass1_f16_sync(src, r, run["reduced"][r], per, g.state, g.workspace, tptrs, sync)
+        elif form == "push":
+            amp.rs_pass1_f16_pushed(src[r], run["push_rows"][r], world, r, run["reduced"][r], per, pieces, g.state,
+                                    g.workspace, tptrs, sync)
         else:
             staging = torch.full((max(1, (world - 1) * per),), 77.0, dtype=torch.float16, device="cuda")
             amp.rs_pass1_f16_ce(src, r, staging, run["reduced"][r], per, pieces, g.state, g.workspace, tptrs, sync)
@@ -205,7 +216,7 @@ def _self_ordered_step(run, arenas, world, per, cfg, form="sm", pieces=3, limit=
         amp.finalize_sums_sync(g.state, run["tables"][r], world, r, cfg, sync, g.history, g.history_len)
     for r, g in enumerate(run["ranks"]):
         dst = [w.data_ptr() + 2 * r * per for w in run["weights"]]
-        if form == "sm":
+        if form in ("sm", "push"):
             amp.pass2_ag_f16(g.master, g.m, g.v, run["reduced"][r], dst, per, r * per, g.tensors, g.ntensors,
                              g.state, cfg.beta1, cfg.beta2, g.eps)
         else:
@@ -249,7 +260,7 @@ def test_self_ordered_parts_and_copy_engine_forms_are_the_fused_kernels_bit_for_
                              g.state, cfg.beta1, cfg.beta2, g.eps)
         _assert_same(_snapshot(run), base, "parts")
 
-        for form in ("sm", "ce"):
+        for form in ("sm", "ce", "push"):
             run = fresh()
             _self_ordered_step(run, arenas, world, per, cfg, form=form, pieces=5)
             _assert_same(_snapshot(run), base, f"self-ordered {form}")
@@ -306,6 +317,15 @@ def test_a_rank_that_never_announces_makes_the_wait_run_out_and_the_step_is_not_
     amp.rs_pass1_f16_ce(src, 0, staging, run["reduced"][0], per, 3, g0.state, g0.workspace, tptrs, sync)
     torch.cuda.synchronize()
     assert amp.zero1_sync_read(run["blocks"][0])[1] == (_lib.PHASE_GRADS + 1) | (1 << 8)
+    assert amp.device_error() == 2
+    assert np.array_equal(H.f16_bits(run["reduced"][0].cpu()), before["reduced"][0])
+    # and so does the owner's side of the pushed form when a peer's piece never arrives
+    for b in run["blocks"]:
+        amp.zero1_sync_init(b)
+    rows = torch.zeros(world * per, dtype=torch.float16, device="cuda")
+    amp.rs_pass1_f16_pushed(src[0], rows, world, 0, run["reduced"][0], per, 2, g0.state, g0.workspace, tptrs, sync)
+    torch.cuda.synchronize()
+    assert amp.zero1_sync_read(run["blocks"][0])[1] == 4 | (1 << 8), "a pushed piece (code 4) of rank 1"
     assert amp.device_error() == 2
     assert np.array_equal(H.f16_bits(run["reduced"][0].cpu()), before["reduced"][0])
     # recovery: state restored by the caller, blocks zeroed; the next step is a correct one
@@ -470,11 +490,14 @@ def _two_gpu_rank(rank, world, port, out_dir):
         slots = param_layout(CONFIGS["readme"])
         cfg = amp.make_schedule(growth_interval=2)
         fused = amp.FusedZero1Optimizer(slots, cfg, loss_scale=65536.0, history_len=16)
-        engines = amp.FusedZero1Optimizer(slots, cfg, loss_scale=65536.0, history_len=16, mover="ce", pieces=5)
+        engines = amp.FusedZero1Optimizer(slots, cfg, loss_scale=65536.0, history_len=16, rs_mover="ce_pull",
+                                          ag_mover="ce", pieces=5)
+        pushed = amp.FusedZero1Optimizer(slots, cfg, loss_scale=65536.0, history_len=16, rs_mover="ce_push",
+                                         ag_mover="sm", pieces=3)
         nccl = amp.ShardedAmpOptimizer(slots, cfg, loss_scale=65536.0, history_len=16)
         gen = torch.Generator().manual_seed(0)
         init = torch.randn(fused.n_params, generator=gen) * 0.02
-        for opt in (fused, engines, nccl):
+        for opt in (fused, engines, pushed, nccl):
             opt.set_params(init)
         single = O.OracleStep(init.numpy(), fused.table, O.make_schedule(growth_interval=2), loss_scale=65536.0,
                               history_len=16)
@@ -487,7 +510,7 @@ def _two_gpu_rank(rank, world, port, out_dir):
                 g = (torch.randn(fused.n, generator=gen) * 1e-3 * scale).half()
                 if k == 2 and rank == 1:
                     g[4242] = float("nan")
-                for opt in (fused, engines, nccl):
+                for opt in (fused, engines, pushed, nccl):
                     opt.grads16.copy_(g)
                     opt.optimizer_step()
                 torch.cuda.synchronize()
@@ -497,11 +520,14 @@ def _two_gpu_rank(rank, world, port, out_dir):
             reduced = torch.zeros(fused.n, dtype=torch.float16, device=fused.device)
             dist.all_gather_into_tensor(reduced, fused.grad_shard)          # test plumbing
             try:
-                # the copy-engine form is the fused form bit for bit
-                assert bytes(engines.read_state()) == bytes(fused.read_state()), k
-                for name in ("grad_shard", "master", "m", "v", "weights16", "pairs"):
-                    assert torch.equal(getattr(engines, name), getattr(fused, name)), (k, name)
-                assert fused.sync_status() == (k + 1, 0) and engines.sync_status() == (k + 1, 0)
+                # the copy-engine forms (pull + push of weights; push of gradients) are the fused form bit for bit
+                for other in (engines, pushed):
+                    assert bytes(other.read_state()) == bytes(fused.read_state()), (k, other.rs_mover)
+                    for name in ("grad_shard", "master", "m", "v", "weights16", "pairs"):
+                        a_bits = getattr(other, name).view(torch.uint8)   # bytes: a NaN sum must compare equal too
+                        assert torch.equal(a_bits, getattr(fused, name).view(torch.uint8)), (k, other.rs_mover, name)
+                    assert other.sync_status() == (k + 1, 0)
+                assert fused.sync_status() == (k + 1, 0)
                 single.step_f16(H2.f16_bits(reduced.cpu()))
                 a, b = fused.read_state(), nccl.read_state()
                 for f in ("loss_scale", "inv_scale", "good_steps", "found_inf", "skipped", "step", "adam_t"):
