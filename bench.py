@@ -45,10 +45,10 @@ BYTES_PASS1 = 2            # per parameter: read the fp16 gradient
 BYTES_PASS2 = 28           # read g16 2 + master 4 + m 4 + v 4; write master 4 + m 4 + v 4 + fp16 weight 2
 BYTES_STEP = BYTES_PASS1 + BYTES_PASS2
 # DRAM traffic of pass 2 per element, from one ncu capture (dram__bytes_read.sum +
-# dram__bytes_write.sum) of a launch on the gpt2-small arena: 1.742693 GB read + 1.686448 GB
+# dram__bytes_write.sum) of a launch on the gpt2-small arena: 1.742767 GB read + 1.684984 GB
 # written over 124,476,416 elements. Every element is touched once, so traffic scales with the
 # element count; the 1.3 B arena is too large to capture under ncu's replay.
-PASS2_DRAM_BYTES_PER_PARAM_NCU = 27.55
+PASS2_DRAM_BYTES_PER_PARAM_NCU = 27.54
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 NVLINK_FALLBACK_GBS = 770.0     # per direction per GPU; used only if the in-run copy measurement fails
