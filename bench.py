@@ -303,6 +303,57 @@ def nvlink_probe(opt, amp, torch, dist, world, rank, max_over_ranks) -> dict:
     return out
 
 
+def mover_sweep(opt, amp, lib, torch, dist, world, max_over_ranks, n, steps=10) -> list:
+    """Per-phase times of the fused ZeRO-1 step with each mover of the NVLink bytes, on the optimizer
+    the timed region used (the settings give the same bits; only who moves the bytes changes):
+    kernel-issued peer loads / stores, copy engines pulling, copy engines pushing, for 2 / 4 / 8
+    pieces and 2 or world - 1 copy streams. CUDA events around the four launches, max over ranks."""
+    from cuda_transformer_b200 import _lib
+    link = (world - 1) / world * 2 * n
+    opt.enable_push()
+    settings = [("sm", "sm", 1, 2)]
+    for rs, ag in (("ce_pull", "sm"), ("ce_push", "sm"), ("sm", "ce"), ("ce_push", "ce")):
+        for pieces in (2, 4, 8):
+            for lanes in sorted(set(min(x, world - 1) for x in (2, 7))):
+                settings.append((rs, ag, pieces, lanes))
+    keep = (opt.rs_mover, opt.ag_mover, opt.pieces)
+    rows = []
+    for rs, ag, pieces, lanes in settings:
+        opt.rs_mover, opt.ag_mover, opt.pieces = rs, ag, pieces
+        _lib.check(lib.b200amp_tune_set(b"ce_lanes", lanes))
+        for _ in range(2):
+            opt.optimizer_step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(steps)]
+        for k in range(steps):
+            ev[k][0].record()
+            opt.fused_pass1()
+            ev[k][1].record()
+            opt.finalize_pairs()
+            ev[k][2].record()
+            opt.fused_pass2()
+            ev[k][3].record()
+            opt.end_step()
+            ev[k][4].record()
+        torch.cuda.synchronize()
+        dist.barrier()
+
+        def avg(i, j):
+            return max_over_ranks(sum(ev[k][i].elapsed_time(ev[k][j]) for k in range(steps)) / steps)
+
+        row = {"rs_mover": rs, "ag_mover": ag, "pieces": pieces, "copy_streams": lanes, "step_ms": avg(0, 4),
+               "rs_ms": avg(0, 1), "finalize_wait_ms": avg(1, 2), "ag_ms": avg(2, 3), "end_barrier_ms": avg(3, 4)}
+        row["rs_nvlink_gbs"] = link / row["rs_ms"] / 1e6
+        row["ag_nvlink_gbs"] = link / row["ag_ms"] / 1e6
+        st = opt.read_state()                       # raises if a wait on another rank gave up
+        row["skipped"] = st.skipped
+        rows.append(row)
+    opt.rs_mover, opt.ag_mover, opt.pieces = keep
+    _lib.check(lib.b200amp_tune_set(b"ce_lanes", 2))
+    return rows
+
+
 def run_gpu(args) -> dict:
     import torch
     import torch.distributed as dist
@@ -605,6 +656,10 @@ def run_gpu(args) -> dict:
         opt.grads16[:8].copy_(saved_head)
         torch.cuda.synchronize()
 
+    sweep = None
+    if world > 1 and fused and args.mover_sweep:
+        sweep = mover_sweep(opt, amp, lib, torch, dist, world, max_over_ranks, n)
+
     parity = None
     if world > 1:
         parity = multi_gpu_parity(opt, amp, torch, dist, world, rank, dev, loss_scale, fused)
@@ -655,6 +710,8 @@ def run_gpu(args) -> dict:
         line["graph_replay"] = graph_replay
     if parity is not None:
         line["parity"] = parity
+    if sweep is not None:
+        line["mover_sweep"] = sweep
     if ref_kernels is not None:
         ref_kernels["speedup"] = ref_kernels["ms_per_step"] / ms_per_step
         line["reference_cuda_kernels"] = ref_kernels
@@ -804,6 +861,9 @@ def main() -> None:
     ap.add_argument("--ag-mover", choices=["sm", "ce"], default="sm",
                     help="N > 1, fused: who moves the all-gather's bytes (the kernel's peer stores, or the copy engines)")
     ap.add_argument("--pieces", type=int, default=4, help="pipelining of the copy-engine movers")
+    ap.add_argument("--mover-sweep", action="store_true",
+                    help="N > 1, fused: after the timed region, time the step's phases with every mover setting "
+                         "(adds `mover_sweep` to the line)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
