@@ -725,16 +725,22 @@ def run_gpu(args) -> dict:
         link_kind = "copy-engine rate between rank pairs measured in this run, both directions busy"
         if link_peak <= 0.0:
             link_peak, link_kind = NVLINK_FALLBACK_GBS, "fallback (the in-run copy measurement failed)"
-        t_hbm = BYTES_PASS2 * n_local / (peak * 1e9)
+        # HBM bytes of the fused pass 2 + all-gather on one GPU: 28 B per element of its own slice, plus
+        # the 2 B per element of every other slice that the peers' stores write into this GPU's arena
+        # while the kernel runs
+        hbm_bytes = BYTES_PASS2 * n_local + 2 * (n - n_local)
+        t_hbm = hbm_bytes / (peak * 1e9)
         t_link = coll_bytes / (link_peak * 1e9)
         by_link = t_link > t_hbm
-        achieved = (coll_bytes if by_link else BYTES_PASS2 * n_local) / (pass2_ms * 1e-3) / 1e9
+        achieved = (coll_bytes if by_link else hbm_bytes) / (pass2_ms * 1e-3) / 1e9
         bound_peak = link_peak if by_link else peak
         line["roofline"].update({
             "bound": "nvlink" if by_link else "hbm",
             "kernel": "pass2_f16_kernel + cudaMemcpyAsync" if args.ag_mover == "ce" else "pass2_ag_f16_kernel",
             "achieved": achieved, "peak": bound_peak, "frac": achieved / bound_peak,
             "peak_kind": link_kind if by_link else f"{peak_kind} copy bandwidth",
+            "algorithmic_bytes_per_launch": coll_bytes if by_link else hbm_bytes,
+            "hbm_bytes_per_launch": hbm_bytes,
             "floor_ms": {"hbm": t_hbm * 1e3, "nvlink": t_link * 1e3}, "traffic": None,
             "traffic_source": None, "nvlink_bytes_per_launch": coll_bytes,
             "rs_pass1_frac_of_link_peak": phases["rs_pass1_nvlink_gbs"] / link_peak})

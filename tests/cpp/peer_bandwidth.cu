@@ -296,6 +296,96 @@ static void run(Mover how, bool read, Side &x, Side &y, bool both, double out[2]
     }
 }
 
+// ---------------------------------------------------------------- SM accesses and a copy engine at once
+//
+// Do kernel-issued peer accesses and a copy engine add up on one link? Both GPUs do the same
+// thing against each other: a kernel moves `sm_bytes` (loads from the peer, or stores to the
+// peer) while a copy engine pushes `ce_bytes` to the peer on a second stream. Reported: the bytes
+// that ARRIVE at a GPU per second (for loads: its own kernel's bytes + the peer's push; for
+// stores: the peer kernel's bytes + the peer's push), slower GPU.
+static double hybrid(Side &x, Side &y, bool sm_reads, long long sm_bytes, long long ce_bytes)
+{
+    Side *sides[2] = {&x, &y};
+    static cudaStream_t copy_stream[2] = {nullptr, nullptr};
+    static cudaEvent_t copy_done[2] = {nullptr, nullptr};
+    for (int k = 0; k < 2; k++)
+    {
+        CK(cudaSetDevice(sides[k]->device));
+        if (copy_stream[k] == nullptr)
+        {
+            CK(cudaStreamCreateWithFlags(&copy_stream[k], cudaStreamNonBlocking));
+            CK(cudaEventCreateWithFlags(&copy_done[k], cudaEventDisableTiming));
+        }
+    }
+    const int reps = 4;
+    for (int pass = 0; pass < 2; pass++)
+    {
+        for (int k = 0; k < 2; k++)
+        {
+            CK(cudaSetDevice(sides[k]->device));
+            CK(cudaEventRecord(sides[k]->begin, sides[k]->stream));
+            CK(cudaStreamWaitEvent(copy_stream[k], sides[k]->begin, 0));
+        }
+        for (int i = 0; i < reps; i++)
+        {
+            for (int k = 0; k < 2; k++)
+            {
+                Side &me = *sides[k], &other = *sides[1 - k];
+                CK(cudaSetDevice(me.device));
+                if (sm_bytes > 0)
+                {
+                    // the kernel uses the lower part of the buffers, the copy engine the upper part
+                    sm_copy<<<SM_GRID, 256, 0, me.stream>>>(reinterpret_cast<const float *>(sm_reads ? other.a : me.a),
+                                                            reinterpret_cast<float *>(sm_reads ? me.b : other.b),
+                                                            sm_bytes / 32);
+                    CK(cudaGetLastError());
+                }
+                if (ce_bytes > 0)
+                {
+                    CK(cudaMemcpyAsync(other.b + BYTES - ce_bytes, me.a + BYTES - ce_bytes, ce_bytes, cudaMemcpyDefault,
+                                       copy_stream[k]));
+                }
+            }
+        }
+        for (int k = 0; k < 2; k++)
+        {
+            CK(cudaSetDevice(sides[k]->device));
+            CK(cudaEventRecord(copy_done[k], copy_stream[k]));
+            CK(cudaStreamWaitEvent(sides[k]->stream, copy_done[k], 0));
+            CK(cudaEventRecord(sides[k]->end, sides[k]->stream));
+        }
+        for (int k = 0; k < 2; k++)
+        {
+            CK(cudaSetDevice(sides[k]->device));
+            CK(cudaStreamSynchronize(sides[k]->stream));
+        }
+    }
+    double slowest = 1e30;
+    for (int k = 0; k < 2; k++)
+    {
+        float ms = 0.0f;
+        CK(cudaEventElapsedTime(&ms, sides[k]->begin, sides[k]->end));
+        const double gbs = static_cast<double>(sm_bytes + ce_bytes) * reps / (ms * 1e-3) / 1e9;
+        slowest = gbs < slowest ? gbs : slowest;
+    }
+    return slowest;
+}
+
+static void hybrid_table(Side &x, Side &y)
+{
+    printf("\nSM accesses and a copy-engine push at once, both GPUs against each other, 1 GiB in total per direction,\n"
+           "GB/s arriving per GPU (SM share of the bytes -> loads | stores)\n");
+    const int shares[] = {100, 85, 75, 65, 50, 0};
+    for (int share : shares)
+    {
+        const long long sm_bytes = BYTES / 100 * share / 4096 * 4096;
+        const long long ce_bytes = (BYTES - sm_bytes) / 4096 * 4096;
+        const double loads = hybrid(x, y, true, sm_bytes, share == 100 ? 0 : ce_bytes);
+        const double stores = hybrid(x, y, false, sm_bytes, share == 100 ? 0 : ce_bytes);
+        printf("hybrid SM %3d %% + copy engine %3d %%  %8.1f | %8.1f\n", share, 100 - share, loads, stores);
+    }
+}
+
 // ---------------------------------------------------------------- all-to-all among R GPUs
 
 constexpr long long SLICE = 256LL << 20;        // bytes each pair of GPUs exchanges per direction
@@ -335,6 +425,32 @@ __global__ void __launch_bounds__(256) a2a_copy(PeerList p, long long n8)
     }
 }
 
+// The same with 128-bit accesses (what a kernel issues when a thread owns 8 fp16 values).
+__global__ void __launch_bounds__(256) a2a_copy_128(PeerList p, long long n4)
+{
+    const long long stride = static_cast<long long>(gridDim.x) * 256;
+    for (long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x; i < n4; i += stride)
+    {
+        float4 v[MAX_R - 1];
+#pragma unroll
+        for (int k = 0; k < MAX_R - 1; k++)
+        {
+            if (k < p.count)
+            {
+                v[k] = reinterpret_cast<const float4 *>(p.src[k])[i];
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < MAX_R - 1; k++)
+        {
+            if (k < p.count)
+            {
+                reinterpret_cast<float4 *>(p.dst[k])[i] = v[k];
+            }
+        }
+    }
+}
+
 struct Node
 {
     char *src = nullptr, *dst = nullptr;        // R slices each: slice q is what goes to / came from GPU q
@@ -342,7 +458,8 @@ struct Node
     cudaEvent_t begin = nullptr, end = nullptr, done[MAX_R - 1] = {};
 };
 
-// mode 0: copy engine pull, 1: copy engine push, 2: SM loads (pull), 3: SM stores (push).
+// mode 0: copy engine pull, 1: copy engine push, 2: SM loads (pull), 3: SM stores (push), 4 and 5: the
+// last two with 128-bit instead of 256-bit accesses.
 // Prints the slowest and the fastest GPU's inbound GB/s.
 static void all_to_all(Node *nodes, int R, int mode, const char *label)
 {
@@ -385,15 +502,22 @@ static void all_to_all(Node *nodes, int R, int mode, const char *label)
                 {
                     PeerList p = {};
                     p.count = R - 1;
+                    const bool pull = mode == 2 || mode == 4;
                     for (int k = 1; k < R; k++)
                     {
                         const int q = (g + k) % R;
-                        p.src[k - 1] = reinterpret_cast<const float *>(mode == 2 ? nodes[q].src + g * SLICE
-                                                                                 : me.src + q * SLICE);
-                        p.dst[k - 1] = reinterpret_cast<float *>(mode == 2 ? me.dst + q * SLICE
-                                                                           : nodes[q].dst + g * SLICE);
+                        p.src[k - 1] = reinterpret_cast<const float *>(pull ? nodes[q].src + g * SLICE
+                                                                            : me.src + q * SLICE);
+                        p.dst[k - 1] = reinterpret_cast<float *>(pull ? me.dst + q * SLICE : nodes[q].dst + g * SLICE);
                     }
-                    a2a_copy<<<148 * 4, 256, 0, me.main>>>(p, SLICE / 32);
+                    if (mode < 4)
+                    {
+                        a2a_copy<<<148 * 4, 256, 0, me.main>>>(p, SLICE / 32);
+                    }
+                    else
+                    {
+                        a2a_copy_128<<<148 * 8, 256, 0, me.main>>>(p, SLICE / 16);
+                    }
                     CK(cudaGetLastError());
                 }
             }
@@ -432,7 +556,7 @@ static void all_to_all(Node *nodes, int R, int mode, const char *label)
 
 static int all_to_all_tables(int count)
 {
-    for (int R = 4; R <= MAX_R && R <= count; R *= 2)
+    for (int R = 2; R <= MAX_R && R <= count; R *= 2)
     {
         for (int a = 0; a < R; a++)
         {
@@ -486,6 +610,8 @@ static int all_to_all_tables(int count)
         all_to_all(nodes, R, 0, "copy engine, pull");
         all_to_all(nodes, R, 1, "copy engine, push");
         all_to_all(nodes, R, 2, "SM loads (pull)");
+        all_to_all(nodes, R, 4, "SM loads, 128-bit");
+        all_to_all(nodes, R, 5, "SM stores, 128-bit");
         all_to_all(nodes, R, 3, "SM stores (push)");
         // the last mode pushed: slice g of GPU q's destination holds GPU g's pattern
         unsigned char got = 0;
@@ -551,6 +677,7 @@ int main()
     {
         return 1;
     }
+    hybrid_table(x, y);
     CK(cudaSetDevice(0));
     CK(cudaFree(x.a));
     CK(cudaFree(x.b));
