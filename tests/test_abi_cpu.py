@@ -136,3 +136,62 @@ def test_tensor_table_check_is_host_only_and_strict(lib):
     with pytest.raises(amp.B200AmpError, match="reaches into"):
         amp.check_tensor_table([(0, 12, 1), (8, 4, 0)])
     amp.check_tensor_table([(0, 8, 1), (8, 8, 0)], 16)
+
+
+def test_new_struct_sizes_match_the_header_as_a_c_compiler_sees_it(tmp_path):
+    """b200amp_zero1_sync and b200amp_decay_runs cross the ABI by pointer from ctypes: their
+    ctypes mirrors must have the size and field offsets gcc gives the header's structs."""
+    import subprocess
+    src = tmp_path / "sizes.c"
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "b200amp.h"\n'
+                   'int main(void) { printf("%zu %zu %zu %zu %zu %d %d\\n", sizeof(b200amp_zero1_sync), '
+                   'offsetof(b200amp_zero1_sync, wait_limit), sizeof(b200amp_decay_runs), '
+                   'offsetof(b200amp_decay_runs, nruns), offsetof(b200amp_decay_runs, flag0), '
+                   'B200AMP_ZERO1_SYNC_BYTES, B200AMP_MAX_RUNS); return 0; }\n')
+    exe = tmp_path / "sizes"
+    subprocess.run(["gcc", "-I", os.path.join(REPO, "include"), str(src), "-o", str(exe)], check=True)
+    got = [int(x) for x in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()]
+    assert got == [C.sizeof(_lib.Zero1Sync), _lib.Zero1Sync.wait_limit.offset, C.sizeof(_lib.DecayRuns),
+                   _lib.DecayRuns.nruns.offset, _lib.DecayRuns.flag0.offset, _lib.ZERO1_SYNC_BYTES, 256]
+
+
+def test_decay_runs_builder_merges_neighbours_with_equal_flags(lib):
+    from cuda_transformer_b200 import amp
+    runs = amp.decay_runs_build([(0, 8, 1), (8, 8, 1), (16, 4, 0), (20, 4, 0), (32, 8, 1)])
+    assert (runs.nruns, runs.flag0, list(runs.first4[:3])) == (3, 1, [0, 4, 8])
+    runs = amp.decay_runs_build([(8, 8, 0)])
+    assert (runs.nruns, runs.flag0, runs.first4[0]) == (1, 0, 2)
+    for name, cfg in CONFIGS.items():
+        slots = param_layout(cfg)
+        r = amp.decay_runs_build(list(tensor_table(slots)))
+        assert r.nruns == 8 * cfg.L + 2 and r.flag0 == 1, name          # wte+wpe | per layer 8 | ln_f joins the last run
+    with pytest.raises(amp.B200AmpError) as err:
+        amp.decay_runs_build([(4 * k, 4, k % 2) for k in range(257)])
+    assert err.value.status == _lib.ERR_LIMIT
+    with pytest.raises(amp.B200AmpError, match="tensor table"):
+        amp.decay_runs_build([(0, 12, 1), (8, 4, 0)])                      # checked like any table
+
+
+def test_pass1_partition_is_a_function_of_n_alone(lib):
+    from cuda_transformer_b200 import amp
+    assert amp.pass1_partition(8) == (1, 8192)
+    assert amp.pass1_partition(8192 * 14 - 8) == (14, 8192)
+    vblocks, per = amp.pass1_partition(1_315_819_520)
+    assert vblocks <= 4736 and per % 8192 == 0 and (vblocks - 1) * per < 1_315_819_520 <= vblocks * per
+    with pytest.raises(amp.B200AmpError):
+        amp.pass1_partition(12)
+
+
+def test_self_ordering_entry_points_refuse_bad_arguments_before_any_launch(lib):
+    """Host-side argument checks only: nothing here reaches a CUDA call."""
+    sync = _lib.Zero1Sync()
+    assert lib.b200amp_zero1_barrier(None, 2, 0, 0, 3, None) == _lib.ERR_ARG
+    assert lib.b200amp_zero1_barrier(C.byref(sync), 3, 0, 0, 3, None) == _lib.ERR_ARG      # 3 ranks
+    assert lib.b200amp_zero1_barrier(C.byref(sync), 2, 2, 0, 3, None) == _lib.ERR_ARG      # rank 2 of 2
+    assert lib.b200amp_zero1_barrier(C.byref(sync), 2, 0, 5, 3, None) == _lib.ERR_ARG      # phase 5
+    assert lib.b200amp_zero1_barrier(C.byref(sync), 2, 0, 0, 0, None) == _lib.ERR_ARG      # nothing to do
+    assert lib.b200amp_zero1_barrier(C.byref(sync), 2, 0, 0, 3, None) == _lib.ERR_ARG      # null flag blocks
+    assert b"flag block" in lib.b200amp_last_error()
+    assert lib.b200amp_zero1_sync_init(None, None) == _lib.ERR_ARG
+    assert lib.b200amp_zero1_sync_read(None, None, None) == _lib.ERR_ARG
+    assert lib.b200amp_copy_async(None, None, 16, None) == _lib.ERR_ARG
