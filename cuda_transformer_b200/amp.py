@@ -35,7 +35,7 @@ __all__ = [
     "initial_state", "begin_step", "unscale_and_norm", "finalize_step", "adamw_multi", "lr_on_gpu",
     "cast_to_x", "CudaGraph", "AmpOptimizer", "Zero1Step", "ShardedAmpOptimizer", "make_schedule",
     "pass1_f16", "pass1_f16_static", "cast_pass1_f32", "pass1_finalize_f16", "rs_pass1_f16", "pass2_ag_f16",
-    "FusedZero1Optimizer", "finalize_sums", "pass2_f16", "step_f16", "check_tensor_table",
+    "FusedZero1Optimizer", "finalize_sums", "pass2_f16", "step_f16", "check_tensor_table", "HostGradientFeed",
     "pass1_partition", "rs_pass1_f16_part", "copy_async", "rs_pass1_f16_ce", "pass2_ag_f16_ce",
     "DecayRuns", "decay_runs_build", "pass2_f16_runs", "Zero1Sync", "make_sync", "zero1_sync_init", "zero1_sync_read", "zero1_barrier", "rs_pass1_f16_sync",
     "finalize_sums_sync", "device_error", "RankWaitError",
@@ -380,7 +380,89 @@ def _tensor_table_device(table: Sequence[Tuple[int, int, int]], device, n: int =
     return host.to(device)
 
 
-class AmpOptimizer:
+class HostGradientFeed:
+    """Steps fed from the host: for a caller whose loss-scaled fp16 gradients arrive in pinned host
+    memory (an offloaded backward pass, a parameter server, a benchmark of the whole path).
+
+        ticket = opt.submit_host_gradients(pinned_fp16)     # returns at once
+        state = opt.collect(ticket)                         # the step's 60-byte state, when it is done
+
+    Two device gradient arenas take turns: while pass 2 of step k reads one, the copy engine fills
+    the other with step k + 1's gradients, so a step costs the longer of its host-to-device copy
+    and its kernels instead of their sum. The copy runs on its own stream; the step (and the
+    device-to-host copy of its state into pinned memory) runs on a second one, behind an event of
+    the copy; an arena is refilled only after the step that read it has finished. At most two
+    steps are in flight: submitting a third collects the first. Mixed into the optimizers below;
+    the host class provides _feed_arenas() and _feed_step(arena_index)."""
+
+    def _feed_setup(self) -> None:
+        dev = self.device
+        with torch.cuda.device(dev):
+            self._feed = {
+                "copy": torch.cuda.Stream(device=dev), "step": torch.cuda.Stream(device=dev),
+                "copied": [torch.cuda.Event() for _ in range(2)], "done": [torch.cuda.Event() for _ in range(2)],
+                "host_state": [torch.empty(C.sizeof(StepState), dtype=torch.uint8, pin_memory=True) for _ in range(2)],
+                "arenas": self._feed_arenas(), "next": 0, "results": {}, "pending": set(),
+            }
+            torch.cuda.current_stream(dev).synchronize()
+
+    def submit_host_gradients(self, host_grads16: torch.Tensor) -> int:
+        if getattr(self, "_feed", None) is None:
+            self._feed_setup()
+        f = self._feed
+        ticket = f["next"]
+        slot = ticket % 2
+        if ticket - 2 in f["pending"]:
+            # its pinned state buffer and its arena are about to be reused: fetch its result now and keep it
+            f["results"][ticket - 2] = self.collect(ticket - 2)
+        arena = f["arenas"][slot]
+        if host_grads16.numel() != arena.numel() or host_grads16.dtype != torch.float16:
+            raise ValueError(f"expected {arena.numel()} fp16 gradients, got {host_grads16.numel()} of {host_grads16.dtype}")
+        with torch.cuda.device(self.device):
+            if ticket == 0:
+                # whatever the caller enqueued on its current stream before the first submission comes first
+                first = torch.cuda.Event()
+                first.record(torch.cuda.current_stream(self.device))
+                f["copy"].wait_event(first)
+                f["step"].wait_event(first)
+            if ticket >= 2:
+                f["copy"].wait_event(f["done"][slot])   # the step that read this arena has finished
+            with torch.cuda.stream(f["copy"]):
+                arena.copy_(host_grads16, non_blocking=True)
+                f["copied"][slot].record(f["copy"])
+            f["step"].wait_event(f["copied"][slot])
+            with torch.cuda.stream(f["step"]):
+                self._feed_step(slot)
+                f["host_state"][slot].copy_(self.state, non_blocking=True)
+                f["done"][slot].record(f["step"])
+        f["pending"].add(ticket)
+        f["next"] = ticket + 1
+        return ticket
+
+    def collect(self, ticket: int) -> StepState:
+        """The state after the step of `ticket` (blocks until that step and its read-back are done)."""
+        f = self._feed
+        if ticket in f["results"]:
+            return f["results"].pop(ticket)
+        if ticket not in f["pending"]:
+            raise ValueError(f"ticket {ticket} was never submitted or has been collected already")
+        slot = ticket % 2
+        f["done"][slot].synchronize()
+        st = StepState.from_buffer_copy(f["host_state"][slot].numpy().tobytes())
+        f["pending"].discard(ticket)
+        return st
+
+    def drain_host_feed(self) -> None:
+        """Waits for every submitted step; results not collected yet stay available to collect()."""
+        f = getattr(self, "_feed", None)
+        if f is None:
+            return
+        for ticket in sorted(f["pending"]):
+            f["results"][ticket] = self.collect(ticket)
+        f["step"].synchronize()
+
+
+class AmpOptimizer(HostGradientFeed):
     """The optimizer state of one GPU that holds the whole arena.
 
     Arenas (flat, in param_layout order, cuda/gpt_fast.cu:96-115): master, m, v (fp32),
@@ -467,6 +549,16 @@ class AmpOptimizer:
             step_f16(self.master, self.m, self.v, self.grads16, self.weights16, self.n, self.tensors,
                      self.ntensors, self.state, self.workspace, self.sched, self.history, self.history_len,
                      self.beta1, self.beta2, self.eps, stream)
+
+    # -- HostGradientFeed
+    def _feed_arenas(self):
+        return [self.grads16, torch.zeros_like(self.grads16)]
+
+    def _feed_step(self, slot: int) -> None:
+        grads = self._feed["arenas"][slot]
+        pass1_finalize_f16(grads, self.n, self.state, self.workspace, self.sched, self.history, self.history_len)
+        pass2_f16(self.master, self.m, self.v, grads, self.weights16, self.n, 0, self.tensors, self.ntensors,
+                  self.state, self.beta1, self.beta2, self.eps)
 
     def read_state(self) -> StepState:
         """Sync + D2H of the 60-byte state (cuda/gpt_fast.cu:461-467). When the staged pass 2 is
@@ -655,7 +747,7 @@ class ShardedAmpOptimizer(Zero1Step):
             super().optimizer_step()
 
 
-class FusedZero1Optimizer(ShardedAmpOptimizer):
+class FusedZero1Optimizer(ShardedAmpOptimizer, HostGradientFeed):
     """ZeRO-1 with the collectives folded into the two passes instead of NCCL calls around them,
     and the ordering between the ranks done by the library's own flag words.
 
@@ -779,6 +871,27 @@ class FusedZero1Optimizer(ShardedAmpOptimizer):
         else:
             pass2_ag_f16(self.master, self.m, self.v, self.grad_shard, self._weight_ptrs, self.n_local, self.begin,
                          self.tensors, self.ntensors, self.state, self.beta1, self.beta2, self.eps)
+
+    # -- HostGradientFeed: a second gradient arena that every rank maps (collective on first use)
+    def _feed_arenas(self):
+        with torch.cuda.device(self.device):
+            alt = self._symm_mem.empty(self.n, dtype=torch.float16, device=self.device)
+            alt.zero_()
+            torch.cuda.current_stream().synchronize()
+            self._handles["grads16_alt"] = self._symm_mem.rendezvous(alt, self._symm_group)
+            shard_bytes = self.begin * 2
+            self._feed_grad_ptrs = [self._grad_ptrs,
+                                    [int(p) + shard_bytes for p in self._handles["grads16_alt"].buffer_ptrs]]
+            self._feed_grads = [self.grads16, alt]
+        return self._feed_grads
+
+    def _feed_step(self, slot: int) -> None:
+        keep_ptrs, keep_arena = self._grad_ptrs, self.grads16
+        self._grad_ptrs, self.grads16 = self._feed_grad_ptrs[slot], self._feed_grads[slot]
+        try:
+            self.optimizer_step()
+        finally:
+            self._grad_ptrs, self.grads16 = keep_ptrs, keep_arena
 
     def end_step(self) -> None:
         zero1_barrier(self.sync, self.world, self.rank, _lib.PHASE_WEIGHTS,

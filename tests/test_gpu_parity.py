@@ -869,3 +869,45 @@ def test_zero_rows_with_zero_gradient_stay_zero(G):
     tail = slice(opt.n_params, opt.n)
     for t in (opt.master, opt.m, opt.v, opt.weights16):
         assert not torch.any(t[tail] != 0)
+
+
+def test_steps_fed_from_pinned_host_memory_equal_the_serial_steps(G):
+    """HostGradientFeed on AmpOptimizer: five steps whose gradients come from pinned host memory
+    through two device arenas taking turns (one with an inf), against the same optimizer stepped
+    serially on the same gradients: every state and every array bit for bit, tickets collected
+    late, early and by the submission of a later step."""
+    from cuda_transformer_b200 import amp
+    from cuda_transformer_b200.layout import CONFIGS, param_layout
+    slots = param_layout(CONFIGS["debug"])
+    cfg = amp.make_schedule(grad_clip=0.5, growth_interval=2)
+    fed = amp.AmpOptimizer(slots, cfg, loss_scale=4096.0, history_len=8)
+    serial = amp.AmpOptimizer(slots, cfg, loss_scale=4096.0, history_len=8)
+    gen = torch.Generator().manual_seed(5)
+    init = torch.randn(fed.n_params, generator=gen) * 0.02
+    fed.set_params(init)
+    serial.set_params(init)
+    batches = []
+    for k in range(5):
+        g = (torch.randn(fed.n, generator=gen) * 1e-3 * 4096.0).half()
+        g[fed.n_params:] = 0
+        if k == 2:
+            g[77] = float("inf")
+        batches.append(g.pin_memory())
+    want = []
+    for g in batches:
+        serial.grads16.copy_(g)
+        serial.optimizer_step()
+        want.append(bytes(serial.read_state()))
+    tickets = [fed.submit_host_gradients(g) for g in batches]       # submitting 2, 3, 4 collects 0, 1, 2 internally
+    assert tickets == [0, 1, 2, 3, 4]
+    got = [bytes(fed.collect(t)) for t in (4, 3)]                   # out of order is fine
+    fed.drain_host_feed()
+    got = [bytes(fed.collect(t)) for t in (0, 1, 2)] + got[::-1]
+    assert got == want
+    with pytest.raises(ValueError):
+        fed.collect(3)
+    assert bytes(fed.read_state()) == want[-1]
+    for a, b in ((fed.master, serial.master), (fed.m, serial.m), (fed.v, serial.v), (fed.weights16, serial.weights16)):
+        assert torch.equal(a, b)
+    st = fed.read_state()
+    assert st.skipped == 1 and st.adam_t == 4
