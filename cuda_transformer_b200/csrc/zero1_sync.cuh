@@ -26,7 +26,7 @@ constexpr int MAX_RANKS = 8;
 constexpr int SYNC_PHASE_GRADS = 0;     // [0..7]   every rank's gradients are in its arena
 constexpr int SYNC_PHASE_PAIRS = 1;     // [8..15]  rank q has written its {sum, flag} pair into every table
 constexpr int SYNC_PHASE_WEIGHTS = 2;   // [16..23] rank q's fp16 weights have landed in every arena
-constexpr int SYNC_EPOCH = 24;          // steps this rank has completed (only the owner writes it)
+constexpr int SYNC_EPOCH = 24;          // number of the last step this rank completed (only the owner writes it)
 constexpr int SYNC_ERROR = 25;          // 0, or what a wait gave up on: (phase + 1) | missing rank << 8
 constexpr int SYNC_STAMP = 26;          // the step in flight, written at its start: what a copy engine copies into
                                         // a peer's PIECE word after the data it announces
@@ -89,10 +89,13 @@ __device__ __forceinline__ bool sync_failed(const SyncArgs &sy)
     return sync_load_relaxed(sync_local(sy) + SYNC_ERROR) != 0;
 }
 
-// The step in flight: one more than the steps completed.
+// The number of the step in flight: one more than the number of the last completed step, and never
+// 0 (the counter wraps from 2^32 - 1 to 1), so a word that is still zero from the set-up never
+// matches a live step.
 __device__ __forceinline__ unsigned int sync_epoch(const SyncArgs &sy)
 {
-    return sync_load_relaxed(sync_local(sy) + SYNC_EPOCH) + 1u;
+    const unsigned int e = sync_load_relaxed(sync_local(sy) + SYNC_EPOCH) + 1u;
+    return e != 0u ? e : 1u;
 }
 
 __device__ __forceinline__ void sync_give_up(const SyncArgs &sy, int phase, int missing_rank)
@@ -108,16 +111,18 @@ __device__ __forceinline__ void sync_signal(const SyncArgs &sy, int phase, int t
     sync_store_release(sy.block[to_rank] + phase * MAX_RANKS + sy.my_rank, e);
 }
 
-// Polls one word of the own block until it has reached e. False when the limit ran out or
-// another thread of this GPU has already given up. The comparison is on the signed difference,
-// so the counter may wrap.
+// Polls one word of the own block until it holds e. False when the limit ran out or another
+// thread of this GPU has already given up. Equality is all the protocol needs: no rank can announce
+// a phase of step e + 1 before every rank has left step e (its own step e ends with a wait for
+// everybody's "weights landed" of step e), so a word never runs ahead of its reader; a stale or
+// wrapped value simply does not match.
 __device__ __forceinline__ bool sync_wait_word(const SyncArgs &sy, int index, unsigned int e)
 {
     const unsigned int *word = sync_local(sy) + index;
     const unsigned int limit = sy.limit != 0 ? sy.limit : SYNC_DEFAULT_LIMIT;
     for (unsigned int tries = 0; tries < limit; tries++)
     {
-        if (static_cast<int>(sync_load_acquire(word) - e) >= 0)
+        if (sync_load_acquire(word) == e)
         {
             return true;
         }

@@ -311,7 +311,8 @@ B200AMP_API int b200amp_pass2_ag_f16(float *master, float *m, float *v, const vo
  * on that on the host, once). A rank announces a phase of the step in flight by storing the
  * step's number into its word of every rank's block; a rank waits by polling its own block. The
  * step's number lives in the block and is advanced on the device, so a step is the same
- * sequence of launches every time. Phases: 0 gradients ready, 1 pairs written, 2 weights
+ * sequence of launches every time. Waits compare for equality and a step number is never 0, so
+ * words still zero from the set-up never match and the 32-bit counter may wrap. Phases: 0 gradients ready, 1 pairs written, 2 weights
  * written.
  * Every wait is bounded (wait_limit polls; 0 = the default, about one second). A wait that runs
  * out records (phase + 1) | missing_rank << 8 in the block's error word, sets bit 1 of
@@ -334,7 +335,8 @@ enum
     B200AMP_SYNC_STAMP = 8      /* record the step in flight where the copy engines read it (b200amp_rs_push_f16_ce) */
 };
 B200AMP_API int b200amp_zero1_sync_init(void *block, b200amp_stream s);
-/* Synchronous read of a rank's own block: steps completed, and the error word (0 = none). */
+/* Synchronous read of a rank's own block: the number of the last step it completed (counts up from 0 and
+ * wraps from 2^32 - 1 to 1), and the error word (0 = none). */
 B200AMP_API int b200amp_zero1_sync_read(const void *block, unsigned int *steps_done, unsigned int *error);
 /* One small kernel: `what` is a combination of the three flags above, applied to `phase` of the
  * step in flight. The step's last launch is (phase 2, SIGNAL | WAIT | ADVANCE): enqueued after

@@ -16,7 +16,10 @@ def test_cpp_host_program_builds():
     from cuda_transformer_b200 import build as lib_build
     lib_build.build()
     exes = build_host_test.build_all()
-    assert [os.path.basename(e) for e in exes] == ["test_amp_host", "test_zero1_host", "peer_bandwidth"]
+    want = ["test_amp_host", "test_zero1_host", "peer_bandwidth"]
+    if build_host_test.nccl_paths() is not None:
+        want.append("test_zero1_nccl_host")
+    assert [os.path.basename(e) for e in exes] == want
     assert all(os.path.exists(e) for e in exes)
 
 
@@ -77,3 +80,26 @@ def test_peer_bandwidth_program_reports_sane_nvlink_figures():
         assert len(table) >= 4, proc.stdout
         for r, label, lo, hi in table:
             assert 100.0 < float(lo) <= float(hi) < 1000.0, (r, label, lo, hi)
+
+
+@pytest.mark.gpu
+def test_cpp_zero1_nccl_host_program_checks_pass():
+    """One process, NCCL around the passes (ncclCommInitAll), R = 2, 4, 8 ranks on as many distinct
+    GPUs as the machine has; with one GPU the program says so and checks nothing."""
+    import torch
+
+    import build_host_test
+    if build_host_test.nccl_paths() is None:
+        pytest.skip("no NCCL headers and library in this environment")
+    exe = build_host_test.build(program="test_zero1_nccl_host")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    proc = subprocess.run([exe], capture_output=True, text=True, timeout=900, env=env)
+    sys.stdout.write(proc.stdout)
+    sys.stderr.write(proc.stderr)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-2000:]
+    if torch.cuda.device_count() < 2:
+        assert "nothing to check" in proc.stdout
+        return
+    assert "all checks passed" in proc.stdout and "FAILED" not in proc.stdout
+    groups = sum(1 for r in (2, 4, 8) if r <= torch.cuda.device_count())
+    assert proc.stdout.count(" ok\n") == groups * 11

@@ -276,6 +276,27 @@ def test_self_ordered_parts_and_copy_engine_forms_are_the_fused_kernels_bit_for_
             assert all(amp.zero1_sync_read(b) == (2, 0) for b in run["blocks"])
 
 
+def test_step_counter_of_the_flag_blocks_may_wrap():
+    """Step numbers are compared for equality and never take the value 0, so the 32-bit counter may
+    wrap: blocks whose last completed step is 2^32 - 2 take three more steps (numbers 2^32 - 1, 1,
+    2; the piece words of the pushed form still zero from the set-up) and match the caller-ordered path."""
+    from cuda_transformer_b200 import amp
+    world, per = 4, 8 * 128 * 33
+    n, init, table, cfg, arenas, fresh = _emulated_setup(world, per, 321)
+    run, base = fresh(), fresh()
+    old = np.zeros(256, dtype=np.uint32)
+    old[:24] = 0xFFFFFFFE                       # the three phases of every rank, as that history leaves them
+    old[24] = 0xFFFFFFFE                        # the last completed step
+    for b in run["blocks"]:
+        b.copy_(torch.from_numpy(old.view(np.int32)).cuda())
+    for k, (form, want) in enumerate((("sm", 0xFFFFFFFF), ("push", 1), ("ce", 2))):
+        _self_ordered_step(run, arenas, world, per, cfg, form=form, pieces=2)
+        _plain_step(base, arenas, world, per, cfg)
+        assert all(amp.zero1_sync_read(b) == (want, 0) for b in run["blocks"]), (k, form)
+    _assert_same(_snapshot(run), _snapshot(base), "three steps across the wrap of the step counter")
+    assert amp.device_error() == 0
+
+
 def test_a_rank_that_never_announces_makes_the_wait_run_out_and_the_step_is_not_applied():
     """Two emulated ranks; rank 1 never announces its gradients (nothing sets its flag). Rank 0's
     kernels give up after a short poll limit, report it, apply nothing, and the context stays
