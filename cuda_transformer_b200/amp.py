@@ -565,6 +565,7 @@ class AmpOptimizer(HostGradientFeed):
         selected (tuning knob pass2_variant = 1) its give-up flag is checked here too: a launch
         that stopped waiting for a bulk copy has updated some tiles only, and the caller must not
         go on with that state."""
+        self.drain_host_feed()          # steps submitted through the host feed run on their own stream
         raw = bytes(self.state.cpu().numpy().tobytes())
         variant = C.c_int()
         check(self.lib.b200amp_tune_get(b"pass2_variant", C.byref(variant)))
@@ -913,6 +914,7 @@ class FusedZero1Optimizer(ShardedAmpOptimizer, HostGradientFeed):
         """The 60-byte state; raises RankWaitError if a kernel of this rank stopped waiting for
         another rank (the step in flight was not applied and the ranks are out of step: restore
         a checkpoint and build the optimizers again)."""
+        self.drain_host_feed()          # steps submitted through the host feed run on their own stream
         st = super().read_state()
         _, error = self.sync_status()
         if error != 0:

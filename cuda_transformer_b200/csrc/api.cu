@@ -67,7 +67,7 @@ int sm_count()
 
 Tunables &tunables()
 {
-    static Tunables t = {4, 2, 1, 256, 0, 6, 0, 8, 0, 16, -1, 2};   // measured best on B200 at the 1.3 B arena
+    static Tunables t = {4, 2, 1, 256, 0, 6, 0, 8, 0, 16, 2};   // measured best on B200 at the 1.3 B arena
     return t;
 }
 
@@ -89,7 +89,6 @@ static const Knob KNOBS[] = {
     {"rs_blocks_per_sm", &Tunables::rs_blocks_per_sm, 1, 32},
     {"ag_blocks_per_sm", &Tunables::ag_blocks_per_sm, 0, 32},
     {"bridge_blocks_per_sm", &Tunables::bridge_blocks_per_sm, 1, 32},
-    {"pass2_carveout", &Tunables::pass2_carveout, -1, 100},
     {"ce_lanes", &Tunables::ce_lanes, 1, 7},
 };
 

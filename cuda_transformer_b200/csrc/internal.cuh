@@ -34,7 +34,6 @@ struct Tunables
     int rs_blocks_per_sm;       // resident CTAs per SM of the fused reduce-scatter + pass 1
     int ag_blocks_per_sm;       // resident CTAs per SM of the fused pass 2 + all-gather, 0 = by rank count
     int bridge_blocks_per_sm;   // CTAs per SM asked for by the fp32 -> fp16 bridge (cast + pass 1)
-    int pass2_carveout;         // -1, or the shared-memory carve-out (percent) asked for pass 2's registers-only kernel
     int ce_lanes;               // copy streams the copy-engine forms of the ZeRO-1 step spread their copies over
 };
 Tunables &tunables();

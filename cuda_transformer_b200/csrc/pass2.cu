@@ -379,16 +379,6 @@ static void launch_registers(int st_hint, int grid, cudaStream_t s, float *maste
                              const b200amp_tensor_info *tensors, int ntensors, const b200amp_step_state *st, float b1,
                              float b2, float eps)
 {
-    // measurement knob: the L1 / shared-memory split asked for (percent of shared memory), applied
-    // when it changes; -1 leaves the driver's choice
-    static int applied_carveout = -1;
-    const int carveout = tunables().pass2_carveout;
-    if (carveout != applied_carveout)
-    {
-        cudaFuncSetAttribute(pass2_f16_kernel<THREADS, 1>, cudaFuncAttributePreferredSharedMemoryCarveout, carveout);
-        cudaFuncSetAttribute(pass2_f16_kernel<THREADS, 0>, cudaFuncAttributePreferredSharedMemoryCarveout, carveout);
-        applied_carveout = carveout;
-    }
     if (st_hint == 1)
     {
         pass2_f16_kernel<THREADS, 1><<<grid, THREADS, 0, s>>>(master, m, v, g16, w16, n8, arena_offset, tensors,
