@@ -187,4 +187,87 @@ struct AmpOptimizer
     }
 };
 
+// Steps fed from pinned host memory, for a host whose loss-scaled fp16 gradients arrive there (an
+// offloaded backward pass, a parameter server). Two device gradient arenas take turns: while pass 2
+// of step k reads one, a copy engine fills the other with step k + 1's gradients on its own stream,
+// so a step costs the longer of its host-to-device copy and its kernels instead of their sum. Each
+// step's 60-byte state is copied into pinned memory behind its pass 2. At most two steps are in
+// flight: submitting a third waits for the first. The reference keeps its gradients on the device
+// (cuda/gpt_fast.cu:452-459) and has no counterpart.
+struct HostGradientFeed
+{
+    AmpOptimizer &opt;
+    DeviceArray<__half> second;                 // the arena that alternates with opt.grads16
+    cudaStream_t copy = nullptr;
+    cudaEvent_t copied[2] = {nullptr, nullptr}, done[2] = {nullptr, nullptr};
+    b200amp_step_state *pinned_state = nullptr; // two of them
+    long long next = 0;
+
+    explicit HostGradientFeed(AmpOptimizer &o) : opt(o), second(static_cast<size_t>(o.n))
+    {
+        B200AMP_HOST_CUDA(cudaSetDevice(opt.device));
+        B200AMP_HOST_CUDA(cudaStreamCreateWithFlags(&copy, cudaStreamNonBlocking));
+        for (int k = 0; k < 2; k++)
+        {
+            B200AMP_HOST_CUDA(cudaEventCreateWithFlags(&copied[k], cudaEventDisableTiming));
+            B200AMP_HOST_CUDA(cudaEventCreateWithFlags(&done[k], cudaEventDisableTiming));
+        }
+        B200AMP_HOST_CUDA(cudaMallocHost(&pinned_state, 2 * sizeof(b200amp_step_state)));
+    }
+    ~HostGradientFeed()
+    {
+        cudaSetDevice(opt.device);
+        cudaStreamSynchronize(opt.stream);
+        cudaStreamSynchronize(copy);
+        cudaFreeHost(pinned_state);
+        for (int k = 0; k < 2; k++)
+        {
+            cudaEventDestroy(copied[k]);
+            cudaEventDestroy(done[k]);
+        }
+        cudaStreamDestroy(copy);
+    }
+    HostGradientFeed(const HostGradientFeed &) = delete;
+    HostGradientFeed &operator=(const HostGradientFeed &) = delete;
+
+    // pinned: opt.n loss-scaled fp16 gradients in page-locked host memory. Returns the step's ticket.
+    long long submit(const __half *pinned)
+    {
+        const long long ticket = next++;
+        const int slot = static_cast<int>(ticket % 2);
+        __half *arena = slot == 0 ? opt.grads16.ptr : second.ptr;
+        B200AMP_HOST_CUDA(cudaSetDevice(opt.device));
+        if (ticket >= 2)
+        {
+            // the step that last read this arena, and the read-back that used this pinned slot, are done
+            B200AMP_HOST_CUDA(cudaEventSynchronize(done[slot]));
+        }
+        B200AMP_HOST_CUDA(cudaMemcpyAsync(arena, pinned, static_cast<size_t>(opt.n) * sizeof(__half),
+                                          cudaMemcpyHostToDevice, copy));
+        B200AMP_HOST_CUDA(cudaEventRecord(copied[slot], copy));
+        B200AMP_HOST_CUDA(cudaStreamWaitEvent(opt.stream, copied[slot], 0));
+        B200AMP_HOST_CHECK(b200amp_step_f16(opt.master.ptr, opt.m.ptr, opt.v.ptr, arena, opt.weights16.ptr, opt.n,
+                                            opt.tensors.ptr, static_cast<int>(opt.tensors.count), opt.state.ptr,
+                                            opt.workspace.ptr, &opt.sched, opt.history.ptr, opt.history_len,
+                                            opt.beta1, opt.beta2, opt.eps, opt.stream));
+        B200AMP_HOST_CUDA(cudaMemcpyAsync(&pinned_state[slot], opt.state.ptr, sizeof(b200amp_step_state),
+                                          cudaMemcpyDeviceToHost, opt.stream));
+        B200AMP_HOST_CUDA(cudaEventRecord(done[slot], opt.stream));
+        return ticket;
+    }
+    // The state after the step of `ticket`; valid for the last two tickets submitted. Blocks until it is there.
+    b200amp_step_state collect(long long ticket)
+    {
+        if (ticket < 0 || ticket >= next || ticket < next - 2)
+        {
+            fprintf(stderr, "error: ticket %lld is not one of the last two of %lld submitted\n", ticket, next);
+            exit(1);
+        }
+        const int slot = static_cast<int>(ticket % 2);
+        B200AMP_HOST_CUDA(cudaSetDevice(opt.device));
+        B200AMP_HOST_CUDA(cudaEventSynchronize(done[slot]));
+        return pinned_state[slot];
+    }
+};
+
 } // namespace b200amp_host

@@ -291,6 +291,59 @@ static void graph_checks()
     check(same_bits(eager.v.download(), graphed.v.download()), "AdamW v after 4 steps: same bits");
 }
 
+static void host_feed_checks()
+{
+    printf("\nsteps fed from pinned host memory (two arenas taking turns) against serial steps\n");
+    const int STEPS = 5;
+    const long long n = 1 << 18;
+    vector<TensorInfo> table = {{0, n / 2, 1}, {n / 2, n / 2, 0}};
+    AmpOptimizer serial(n, table, flat_schedule(2), 1e-8f, 4096.0f);
+    AmpOptimizer fed(n, table, flat_schedule(2), 1e-8f, 4096.0f);
+    vector<float> init = randn(n, 0.02f, 21);
+    serial.set_params(init);
+    fed.set_params(init);
+    __half *pinned = nullptr;
+    B200AMP_HOST_CUDA(cudaMallocHost(&pinned, STEPS * n * sizeof(__half)));
+    vector<StepState> want;
+    for (int k = 0; k < STEPS; k++)
+    {
+        vector<__half> g16;
+        scaled_fp16_values(randn(n, 1e-3f, 30 + k), 4096.0f, &g16);
+        if (k == 2)
+        {
+            g16[777] = __float2half(INFINITY);
+        }
+        memcpy(pinned + k * n, g16.data(), n * sizeof(__half));
+        serial.set_grads(g16);
+        serial.optimizer_step();
+        want.push_back(serial.read_state());
+    }
+    bool states_same = true;
+    {
+        b200amp_host::HostGradientFeed feed(fed);
+        long long last = -1;
+        for (int k = 0; k < STEPS; k++)
+        {
+            const long long ticket = feed.submit(pinned + k * n);
+            if (last >= 0)
+            {
+                const StepState got = feed.collect(last);
+                states_same = states_same && memcmp(&got, &want[last], sizeof(got)) == 0;
+            }
+            last = ticket;
+        }
+        const StepState got = feed.collect(last);
+        states_same = states_same && memcmp(&got, &want[last], sizeof(got)) == 0;
+    }
+    B200AMP_HOST_CUDA(cudaFreeHost(pinned));
+    check(states_same, "every step's 60 state bytes equal the serial run's (one skipped step of five)");
+    check(same_bits(serial.master.download(), fed.master.download()), "parameters after 5 steps: same bits");
+    check(same_bits(serial.m.download(), fed.m.download()) && same_bits(serial.v.download(), fed.v.download()),
+          "AdamW m and v after 5 steps: same bits");
+    const StepState st = fed.read_state();
+    check(st.skipped == 1 && st.adam_t == 4 && st.step == 5, "one skipped step, four applied");
+}
+
 int main()
 {
     static_assert(sizeof(StepState) == 60, "StepState is the reference's 60-byte checkpoint ABI");
@@ -303,6 +356,7 @@ int main()
     scaler_checks();
     native_against_compat();
     graph_checks();
+    host_feed_checks();
     printf("\n%s\n", g_failed == 0 ? "all checks passed" : "SOME CHECKS FAILED");
     return g_failed == 0 ? 0 : 1;
 }
