@@ -582,7 +582,7 @@ def run_gpu(args) -> dict:
         e2e_run(2)                                  # both arenas touched, streams and mappings set up
         opt.drain_host_feed()
         barrier()
-        copy_stream, step_stream = opt._feed["copy"], opt._feed["step"]
+        copy_stream, step_stream = opt.host_feed_streams()
         e0 = torch.cuda.Event(enable_timing=True)
         e1 = torch.cuda.Event(enable_timing=True)
         e0.record(copy_stream)

@@ -452,6 +452,12 @@ class HostGradientFeed:
         f["pending"].discard(ticket)
         return st
 
+    def host_feed_streams(self):
+        """(copy stream, step stream) of the feed, for a caller that wants to put its own events on them."""
+        if getattr(self, "_feed", None) is None:
+            self._feed_setup()
+        return self._feed["copy"], self._feed["step"]
+
     def drain_host_feed(self) -> None:
         """Waits for every submitted step; results not collected yet stay available to collect()."""
         f = getattr(self, "_feed", None)
