@@ -782,7 +782,7 @@ class FusedZero1Optimizer(ShardedAmpOptimizer, HostGradientFeed):
     (peer stores of the kernel) or "ce" (pieces pushed under pass 2, b200amp_pass2_ag_f16_ce).
     `pieces` sets the pipelining of the copy-engine forms.
 
-    Every wait is bounded (about ten seconds by default; `wait_limit` polls). A rank that never shows up makes
+    Every wait is bounded (several seconds by default; `wait_limit` polls). A rank that never shows up makes
     the others' kernels return without applying the step; read_state() then raises
     RankWaitError naming the phase and the missing rank. The averaged gradient is rounded to
     fp16 once from an fp32 sum, so it is at least as accurate as an fp16 NCCL reduction; norm and

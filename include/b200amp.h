@@ -314,7 +314,7 @@ B200AMP_API int b200amp_pass2_ag_f16(float *master, float *m, float *v, const vo
  * sequence of launches every time. Waits compare for equality and a step number is never 0, so
  * words still zero from the set-up never match and the 32-bit counter may wrap. Phases: 0 gradients ready, 1 pairs written, 2 weights
  * written.
- * Every wait is bounded (wait_limit polls; 0 = the default, about ten seconds). A wait that runs
+ * Every wait is bounded (wait_limit polls; 0 = the default, several seconds). A wait that runs
  * out records (phase + 1) | missing_rank << 8 in the block's error word, sets bit 1 of
  * b200amp_device_error, and the kernel returns without doing its work; kernels launched after
  * it see the error word and return at once, the finalize sets found_inf = 1 so that pass 2

@@ -311,7 +311,14 @@ def test_a_rank_that_never_announces_makes_the_wait_run_out_and_the_step_is_not_
     tptrs = [t.data_ptr() for t in run["tables"]]
     src = [a.data_ptr() for a in arenas]
     assert amp.device_error() == 0
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
     amp.rs_pass1_f16_sync(src, 0, run["reduced"][0], per, g0.state, g0.workspace, tptrs, sync)
+    t1.record()
+    torch.cuda.synchronize()
+    gave_up_after_ms = t0.elapsed_time(t1)
+    print(f"a wait of 2000 polls gave up after {gave_up_after_ms:.3f} ms ({gave_up_after_ms / 2000 * 1e3:.2f} us per poll)")
+    assert gave_up_after_ms < 100.0, "2000 polls must be a matter of milliseconds"
     amp.finalize_sums_sync(g0.state, run["tables"][0], world, 0, cfg, sync, g0.history, g0.history_len)
     dst = [w.data_ptr() for w in run["weights"]]
     amp.pass2_ag_f16(g0.master, g0.m, g0.v, run["reduced"][0], dst, per, 0, g0.tensors, g0.ntensors, g0.state,
