@@ -14,7 +14,10 @@ Two layers:
   gradient arena the native kernels read. ShardedAmpOptimizer is the ZeRO-1 form over
   torch.distributed: reduce-scatter of fp16 gradients, the two passes on the rank's
   shard, an all-gather of the 16-byte {norm^2, flag} pairs, and an in-place
-  all-gather of the fp16 weights.
+  all-gather of the fp16 weights. FusedZero1Optimizer folds the two collectives into
+  the passes (peer loads and stores over NVLink, or the copy engines) and orders the
+  ranks with the library's own bounded flag words. HostGradientFeed (mixed into the
+  owners) feeds steps from pinned host memory through two gradient arenas taking turns.
 
 torch is used for device memory, streams and the process group only; every
 arithmetic step runs in the CUDA kernels of the library.
