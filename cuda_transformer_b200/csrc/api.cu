@@ -108,7 +108,7 @@ extern "C" B200AMP_API const char *b200amp_last_error(void)
 
 extern "C" B200AMP_API const char *b200amp_version(void)
 {
-    return "0.1.0";
+    return "0.2.0";
 }
 
 extern "C" B200AMP_API int b200amp_device_check(void)
